@@ -1,0 +1,419 @@
+"""CPU oracle for the SpargeAttn sparse-attention hot path.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in plain PyTorch on the CPU, the arithmetic of the reference's
+`spas_sage2_attn_meansim_topk_cuda` / `block_sparse_sage2_attn_cuda` path.  Only tests,
+the smoke check and the CPU-baseline leg of the benchmark may import it; the product
+(`spargeattn_b200`) never does and fails loudly without its CUDA library.
+
+Parity status: **parity unpinned**.  The reference ships no tests, golden vectors or stored
+input/output pairs for this path, and its own kernels need a GPU, so this restatement is
+pinned only against (a) the reference's Triton kernels run under the Triton CPU interpreter
+for fp16 inputs (tests/golden/make_golden.py records those fixtures) and (b) itself.
+
+Where the reference leaves a summation order or a division instruction to a library
+(Triton reductions, cuBLAS, torch softmax/sort), this file pins one choice, stated at each
+function, and the CUDA kernels implement the same choice so that they can be compared
+bit for bit:
+  * reductions over rows / channels accumulate in fp64 (order-free to ~1e-16) and are
+    rounded to fp32 once;
+  * fp32 divisions are IEEE round-to-nearest;
+  * the pooled score is an fp32 FMA chain over ascending channel index;
+  * the row softmax is evaluated in fp64, rounded to fp32, then to the 16-bit dtype;
+  * top-k uses a stable descending order (ties -> lower block index).
+
+Reference files are cited as path:line relative to the reference project root.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+BLKQ = 128
+BLKK = 64
+S_FP8_OFFSET = 8.807          # csrc/qattn/attn_utils.cuh:28-30
+V_SCALE_MAX = 2.25            # spas_sage_attn/core.py:151
+LOG2E = 1.4426950408889634    # csrc/math.cuh
+MASK_VALUE = -5000000.0       # csrc/qattn/attn_utils.cuh:348-352
+
+
+# ----------------------------------------------------------------------------- helpers
+def hyperparameter_check(hyper, H: int) -> torch.Tensor:
+    """spas_sage_attn/utils.py:38-50 -- scalar / 0-d / 1-d -> fp32 [H]."""
+    if type(hyper) in (float, int):
+        return torch.full((H,), float(hyper), dtype=torch.float32)
+    if isinstance(hyper, torch.Tensor):
+        assert hyper.dim() <= 1, "Hyperparameter tensor must be 1D"
+        if hyper.dim() == 0:
+            return torch.full((H,), hyper.item(), dtype=torch.float32)
+        assert hyper.numel() == H, f"Hyperparameter tensor must have {H} elements, but has {hyper.numel()}"
+        return hyper.to(torch.float32).cpu()
+    raise ValueError("Hyperparameter must be a float or a tensor")
+
+
+def precision_metric(a: torch.Tensor, b: torch.Tensor) -> dict:
+    """spas_sage_attn/utils.py:25-36 -- cosine similarity, relative L1, RMSE (b is the reference)."""
+    x, xx = a.double().reshape(1, -1), b.double().reshape(1, -1)
+    sim = torch.nn.functional.cosine_similarity(x, xx).item()
+    l1 = ((x - xx).abs().sum() / xx.abs().sum()).item()
+    rmse = torch.sqrt(torch.mean((x - xx) ** 2)).item()
+    return {"Cossim": sim, "L1": l1, "RMSE": rmse}
+
+
+def e4m3_round(x: torch.Tensor) -> torch.Tensor:
+    """fp32 -> e4m3 value (returned as fp32), round-to-nearest-even, saturating to +-448.
+
+    Follows `cvt.rn.satfinite.e4m3x2.f32` as used at csrc/numeric_conversion.cuh:48-63.  Written
+    out by hand because torch's CPU float8 cast does not saturate."""
+    x = x.to(torch.float32)
+    s = torch.sign(x)
+    a = x.abs().clamp(max=448.0)
+    # exponent of the e4m3 bucket: normal numbers have 3 mantissa bits, subnormals a fixed 2^-9 step
+    e = torch.floor(torch.log2(torch.where(a > 0, a, torch.ones_like(a))))
+    e = e.clamp(min=-6.0)
+    step = torch.exp2(e - 3.0)
+    q = torch.round(a / step) * step          # torch.round is half-to-even; a/step is exact (power of two)
+    q = q.clamp(max=448.0)
+    return torch.where(a > 0, s * q, torch.zeros_like(a) * s)
+
+
+def e4m3_bits(x: torch.Tensor) -> torch.Tensor:
+    """e4m3-representable fp32 values -> their uint8 bit patterns."""
+    return x.to(torch.float32).to(torch.float8_e4m3fn).view(torch.uint8)
+
+
+def e4m3_from_bits(b: torch.Tensor) -> torch.Tensor:
+    return b.view(torch.float8_e4m3fn).to(torch.float32)
+
+
+# ----------------------------------------------------------------------------- K mean
+def k_mean(k: torch.Tensor) -> torch.Tensor:
+    """spas_sage_attn/core.py:119-120 `km = k.mean(dim=-2, keepdim=True)` in k's dtype.
+
+    Pinned: exact (fp64) sum over tokens, divided by N in fp64, rounded to fp32, then to the
+    16-bit dtype.  torch's own reduction accumulates in fp32 in a library-chosen order."""
+    n = k.shape[-2]
+    return (k.double().sum(dim=-2, keepdim=True) / float(n)).float().to(k.dtype)
+
+
+# ----------------------------------------------------------------------------- pool / sim / quant
+def _blocks(x: torch.Tensor, bs: int) -> Tuple[torch.Tensor, torch.Tensor, int]:
+    """[B,H,N,D] -> zero-padded [B,H,nb,bs,D] plus a row-validity mask [nb,bs]."""
+    B, H, N, D = x.shape
+    nb = (N + bs - 1) // bs
+    pad = nb * bs - N
+    if pad:
+        x = torch.cat([x, torch.zeros(B, H, pad, D, dtype=x.dtype)], dim=2)
+    valid = (torch.arange(nb * bs) < N).view(nb, bs)
+    return x.view(B, H, nb, bs, D), valid, nb
+
+
+def pool_sim_quant(x: torch.Tensor, km: Optional[torch.Tensor], bs: int, simthreshd1: torch.Tensor,
+                   want_pool: bool = True):
+    """spas_sage_attn/utils.py:161-214 (fused pool + self-similarity + per-block INT8) and
+    utils.py:89-159 (`qk_quantize`, quantiser only).
+
+    x: [B,H,N,D] fp16/bf16.  km: [B,H,1,D] in x's dtype or None.  Returns
+    (pool [B,H,nb,D] x.dtype, sim [B,H,nb] bool, x_int8 [B,H,N,D], scale [B,H,nb] fp32)."""
+    B, H, N, D = x.shape
+    xb, valid, nb = _blocks(x, bs)
+    if km is not None:
+        # utils.py:185-188: subtraction in the 16-bit dtype, padded rows re-zeroed
+        xb = (xb - km.view(B, H, 1, 1, D)).to(x.dtype)
+        xb = torch.where(valid.view(1, 1, nb, bs, 1), xb, torch.zeros((), dtype=x.dtype))
+    x32 = xb.float()
+
+    # utils.py:206-210 -- scale = max|x| / 127 + 1e-7 ; round half away from zero
+    amax = x32.abs().amax(dim=(-1, -2))
+    scale = amax / 127.0 + 1e-7
+    y = x32 / scale.view(B, H, nb, 1, 1)
+    y = y + torch.where(y >= 0, 0.5, -0.5).to(torch.float32)
+    x_int8 = y.to(torch.int8).view(B, H, nb * bs, D)[:, :, :N].contiguous()
+    if not want_pool:
+        return None, None, x_int8, scale
+
+    # utils.py:182,192 -- pool = sum over rows / BS_  (BS_ = rows actually present)
+    bs_ = valid.sum(-1).to(torch.float32)                            # [nb]
+    pool = (x32.double().sum(dim=-2).float() / bs_.view(1, 1, nb, 1)).to(x.dtype)
+
+    # utils.py:193-199 -- x_hat = fp16(x / ||x||), sim = sum_ij <x_hat_i, x_hat_j> / BS_^2 > thr
+    # using  sum_ij <a_i, a_j> = || sum_i a_i ||^2 .
+    nrm = (x32.double() ** 2).sum(dim=-1, keepdim=True).float().sqrt()
+    xhat = (x32 / nrm).to(torch.float16)                             # 0/0 -> NaN on empty rows
+    ssum = xhat.double().sum(dim=-2)                                 # [B,H,nb,D]
+    total = (ssum * ssum).sum(dim=-1).float()
+    simval = total / (bs_ * bs_).view(1, 1, nb)
+    sim = simval > simthreshd1.view(1, H, 1)                          # NaN compares False
+    full = (valid.sum(-1) == bs).view(1, 1, nb)
+    zero_row = (nrm.squeeze(-1) == 0).any(dim=-1)
+    sim = sim & full & ~zero_row                                     # explicit form of the NaN rule
+    return pool, sim, x_int8, scale
+
+
+# ----------------------------------------------------------------------------- predictor
+def pooled_probs(pq: torch.Tensor, pk: torch.Tensor, sim_k: torch.Tensor, is_causal: bool) -> torch.Tensor:
+    """spas_sage_attn/utils.py:386-396 -- pooled score map and its row softmax, in the 16-bit dtype."""
+    B, H, nq, D = pq.shape
+    nk = pk.shape[2]
+    dt = pq.dtype
+    a, b = pq.float(), pk.float()
+    acc = torch.zeros(B, H, nq, nk, dtype=torch.float32)
+    for d in range(D):  # fp32 FMA chain, ascending d (16-bit x 16-bit products are exact in fp32)
+        acc = acc + a[..., :, d:d + 1] * b[..., :, d].unsqueeze(-2)
+    s = acc.to(dt)
+    s = (s.float() * torch.tensor(D ** -0.5, dtype=torch.float32)).to(dt)
+    s = s.masked_fill(~sim_k.view(B, H, 1, nk), float("-inf"))
+    if is_causal:
+        qi = torch.arange(nq).view(nq, 1)
+        kj = torch.arange(nk).view(1, nk)
+        s = s.masked_fill((kj >= (qi + 1) * (BLKQ // BLKK)).view(1, 1, nq, nk), float("-inf"))
+    s64 = s.double()
+    m = s64.amax(dim=-1, keepdim=True)
+    e = torch.exp(s64 - m)
+    p = (e / e.sum(dim=-1, keepdim=True)).float().to(dt)
+    p = torch.where(torch.isinf(m), torch.zeros((), dtype=dt), p)     # row with no candidate
+    return p
+
+
+def select_blocks(p: torch.Tensor, sim_q: torch.Tensor, sim_k: torch.Tensor, topk: Optional[torch.Tensor],
+                  cdfthreshd: Optional[torch.Tensor], is_causal: bool, attention_sink: bool) -> torch.Tensor:
+    """spas_sage_attn/utils.py:397-415 and :282-292 -- final boolean block map [B,H,nq,nk]."""
+    B, H, nq, nk = p.shape
+    order = torch.sort(p.float(), dim=-1, descending=True, stable=True)
+    if cdfthreshd is not None:
+        # utils.py:398-403: cumulative sum of the sorted probabilities, kept in the 16-bit dtype.
+        cdf = torch.cumsum(order.values, dim=-1).to(p.dtype).float()
+        thr = cdfthreshd.view(1, H, 1, 1).expand(B, H, nq, 1).contiguous()
+        n_sel = torch.searchsorted(cdf, thr, right=True).squeeze(-1)
+    else:
+        n_sel = (topk.to(torch.float32) * nk).to(torch.int64).view(1, H, 1).expand(B, H, nq)
+    n_sel = n_sel.clamp(min=1, max=nk)                                # utils.py:289 (>= 1)
+    rank = torch.empty_like(order.indices)
+    rank.scatter_(-1, order.indices, torch.arange(nk).expand(B, H, nq, nk).contiguous())
+    sel = rank < n_sel.unsqueeze(-1)
+    fmap = sel | ~sim_k.view(B, H, 1, nk) | ~sim_q.view(B, H, nq, 1)
+    if is_causal:
+        qi = torch.arange(nq).view(nq, 1)
+        kj = torch.arange(nk).view(1, nk)
+        fmap = fmap & (kj < (qi + 1) * (BLKQ // BLKK)).view(1, 1, nq, nk)
+    if attention_sink:
+        fmap = fmap.clone()
+        fmap[..., 0] = True
+    return fmap
+
+
+def block_map_to_lut(block_map: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """spas_sage_attn/utils.py:54-87 -- delta-encoded LUT (first entry absolute, zero tail) + counts."""
+    bm = block_map != 0
+    B, H, nq, nk = bm.shape
+    valid = bm.sum(-1).to(torch.int32)
+    idx = torch.arange(nk).expand(B, H, nq, nk)
+    key = torch.where(bm, idx, idx + nk)                               # live first, ascending
+    order = torch.sort(key, dim=-1, stable=True).indices
+    pos = torch.gather(idx, -1, order)
+    prev = torch.cat([torch.zeros(B, H, nq, 1, dtype=pos.dtype), pos[..., :-1]], dim=-1)
+    lut = pos - prev
+    live = torch.arange(nk).view(1, 1, 1, nk) < valid.unsqueeze(-1)
+    lut = torch.where(live, lut, torch.zeros_like(lut)).to(torch.int32)
+    return lut, valid
+
+
+def block_map_to_mask(block_map: torch.Tensor, nq_tokens: int, nk_tokens: int) -> torch.Tensor:
+    """spas_sage_attn/utils.py:424-432 -- expand a block map to a token mask, cropped to the lengths."""
+    m = (block_map != 0).repeat_interleave(BLKQ, dim=-2).repeat_interleave(BLKK, dim=-1)
+    return m[..., :nq_tokens, :nk_tokens]
+
+
+def predictor(q, k, km, is_causal=False, simthreshd1=-0.1, cdfthreshd=None, topk=0.5, attention_sink=False):
+    """spas_sage_attn/utils.py:371-421 `get_block_map_meansim_fuse_quant`.
+    Returns dict(map, lut, valid, q_int8, q_scale, k_int8, k_scale, pq, pk, sim_q, sim_k, p)."""
+    assert (cdfthreshd is None) != (topk is None), "Only one of cdfthreshd and topk can be set."
+    H = q.shape[1]
+    thr = hyperparameter_check(simthreshd1, H)
+    tk = hyperparameter_check(topk, H) if topk is not None else None
+    cdf = hyperparameter_check(cdfthreshd, H) if cdfthreshd is not None else None
+    pq, sim_q, q8, qs = pool_sim_quant(q, None, BLKQ, thr)
+    pk, sim_k, k8, ks = pool_sim_quant(k, km, BLKK, thr)
+    p = pooled_probs(pq, pk, sim_k, is_causal)
+    fmap = select_blocks(p, sim_q, sim_k, tk, cdf, is_causal, attention_sink)
+    lut, valid = block_map_to_lut(fmap)
+    return dict(map=fmap, lut=lut, valid=valid, q_int8=q8, q_scale=qs, k_int8=k8, k_scale=ks,
+                pq=pq, pk=pk, sim_q=sim_q, sim_k=sim_k, p=p)
+
+
+# ----------------------------------------------------------------------------- V quantisation
+def quant_v(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """spas_sage_attn/core.py:115-117,143-151 + csrc/fused/fused.cu:80-191.
+
+    v: [B,H,N,D] any float dtype.  Returns (v8 [B,H,N_pad128,D] as e4m3 values in fp32, zero rows
+    beyond N; v_scale [B,H,D] fp32).  The reference stores the same numbers transposed to
+    [B,H,D,N_pad] with a 16-token permutation that only serves its mma.sync register layout."""
+    B, H, N, D = v.shape
+    v16 = v.to(torch.float16).float()
+    amax = v16.abs().amax(dim=-2)                                     # [B,H,D]
+    v_scale = amax / V_SCALE_MAX
+    r = V_SCALE_MAX / amax
+    r = torch.where(amax > 0, r, torch.zeros_like(r))                 # all-zero channel: emit zeros, not NaN
+    v8 = e4m3_round(v16 * r.unsqueeze(-2))
+    npad = (N + 127) // 128 * 128
+    out = torch.zeros(B, H, npad, D, dtype=torch.float32)
+    out[:, :, :N] = v8
+    return out, v_scale
+
+
+# ----------------------------------------------------------------------------- attention
+def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_scale: float, pvthreshd,
+                        token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True):
+    """Oracle B: block-online emulation of csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:42-755 with the
+    helpers of csrc/qattn/attn_utils.cuh (update_mo :418-466, exponentiate_r :391-415,
+    RS_32_to_8 :581-596, normalize_d :757-811).  fp32 PV accumulation.
+
+    q8,k8: int8 [B,H,N,D]; q_scale [B,H,nq]; k_scale [B,H,nk]; v8: e4m3 values fp32 [B,H,N_pad,D];
+    v_scale [B,H,D]; block_map bool [B,H,nq,nk]; pvthreshd fp32 [H]."""
+    B, H, N, D = q8.shape
+    nq, nk = block_map.shape[-2:]
+    c = sm_scale * LOG2E
+    o = torch.zeros(B, H, N, D, dtype=torch.float32)
+    skipped = 0
+    for b in range(B):
+        for h in range(H):
+            kf = k8[b, h].float()
+            for i in range(nq):
+                r0, r1 = i * BLKQ, min((i + 1) * BLKQ, N)
+                qf = q8[b, h, r0:r1].float()
+                rows = r1 - r0
+                m = torch.full((rows,), MASK_VALUE, dtype=torch.float32)
+                d = torch.ones(rows, dtype=torch.float32)
+                acc = torch.zeros(rows, D, dtype=torch.float32)
+                live = torch.nonzero(block_map[b, h, i]).flatten().tolist()
+                for n_it, j in enumerate(live):
+                    c0, c1 = j * BLKK, min((j + 1) * BLKK, N)
+                    s = qf @ kf[c0:c1].t()                              # exact: |S| < 2^24
+                    t = s * (c * q_scale[b, h, i] * k_scale[b, h, j])
+                    if token_causal:
+                        qi = torch.arange(r0, r1).view(-1, 1)
+                        kj = torch.arange(c0, c1).view(1, -1)
+                        t = torch.where(kj > qi, torch.full_like(t, MASK_VALUE), t)
+                    rowmax = t.amax(dim=-1)
+                    m_new = torch.maximum(m, rowmax)
+                    is_tail = n_it >= len(live) - 2                    # last two live blocks never skip
+                    if pv_skip and not is_tail:
+                        delta = (rowmax - m).max().item()
+                        if delta + float(pvthreshd[h]) <= 0:
+                            skipped += 1
+                            continue
+                    alpha = torch.exp2(m - m_new)
+                    d = d * alpha
+                    acc = acc * alpha.unsqueeze(-1)
+                    m = m_new
+                    p = torch.exp2(t - m.unsqueeze(-1) + S_FP8_OFFSET)
+                    d = d + p.sum(dim=-1)
+                    p8 = e4m3_round(p)
+                    acc = acc + p8 @ v8[b, h, c0:c1]
+                if live:
+                    o[b, h, r0:r1] = acc / d.unsqueeze(-1) * v_scale[b, h].view(1, D)
+    return o.to(out_dtype), skipped
+
+
+def attention_dense_masked(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_scale: float,
+                           token_causal: bool = False, out_dtype=torch.bfloat16, q_chunk: int = 1024):
+    """Oracle A: fp32 softmax attention on the de-quantised operands with the 128x64 block map
+    expanded to tokens (spas_sage_attn/utils.py:424-432).  No fp8 rounding of P, no PV skip.
+    Also the CPU baseline that the benchmark times."""
+    B, H, N, D = q8.shape
+    nq, nk = block_map.shape[-2:]
+    qd = q8.float() * q_scale.repeat_interleave(BLKQ, dim=-1)[..., :N].unsqueeze(-1)
+    kd = k8.float() * k_scale.repeat_interleave(BLKK, dim=-1)[..., :N].unsqueeze(-1)
+    vd = v8[:, :, :N] * v_scale.unsqueeze(-2)
+    o = torch.zeros(B, H, N, D, dtype=torch.float32)
+    for r0 in range(0, N, q_chunk):
+        r1 = min(r0 + q_chunk, N)
+        assert r0 % BLKQ == 0
+        bm = block_map[:, :, r0 // BLKQ:(r1 + BLKQ - 1) // BLKQ]
+        mask = block_map_to_mask(bm, r1 - r0, N)
+        if token_causal:
+            qi = torch.arange(r0, r1).view(-1, 1)
+            kj = torch.arange(N).view(1, -1)
+            mask = mask & (kj <= qi)
+        s = torch.matmul(qd[:, :, r0:r1], kd.transpose(-1, -2)) * sm_scale
+        s = s.masked_fill(~mask, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        p = torch.nan_to_num(p, nan=0.0)                                # rows with no live block -> zeros
+        o[:, :, r0:r1] = torch.matmul(p, vd)
+    return o.to(out_dtype)
+
+
+# ----------------------------------------------------------------------------- public API mirrors
+def _prologue(q, k, v, tensor_layout):
+    """spas_sage_attn/core.py:107-117 -- layout, N>=128 check, dtype normalisation."""
+    assert tensor_layout in ["HND", "NHD"]
+    if tensor_layout == "NHD":
+        q, k, v = (t.transpose(-2, -3) for t in (q, k, v))
+    assert q.size(-2) >= 128, "seq_len should be not less than 128."
+    dt = torch.float16 if q.dtype in (torch.float32, torch.float16) else torch.bfloat16
+    return q.contiguous().to(dt), k.contiguous().to(dt), v.contiguous().to(torch.float16), dt
+
+
+def spas_sage2_attn_meansim_topk(q, k, v, is_causal=False, scale=None, smooth_k=True, simthreshd1=-0.1,
+                                 cdfthreshd=None, topk=0.5, pvthreshd=50, attention_sink=False,
+                                 tensor_layout="HND", return_sparsity=False, token_causal=False,
+                                 blockwise=True, return_parts=False):
+    """spas_sage_attn/core.py:105-169 (and :39-103 when `cdfthreshd` is given instead of `topk`).
+    `token_causal=False` reproduces the reference, which never forwards is_causal to its kernel."""
+    q, k, v, dt = _prologue(q, k, v, tensor_layout)
+    H, D = q.shape[1], q.shape[-1]
+    assert D in (64, 128)
+    km = k_mean(k) if smooth_k else None
+    pr = predictor(q, k, km, is_causal, simthreshd1, cdfthreshd, topk, attention_sink)
+    sm_scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    pv = hyperparameter_check(pvthreshd, H)
+    v8, vs = quant_v(v)
+    if blockwise:
+        o, _ = attention_blockwise(pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v8, vs, pr["map"],
+                                   sm_scale, pv, token_causal and is_causal, dt)
+    else:
+        o = attention_dense_masked(pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v8, vs, pr["map"],
+                                   sm_scale, token_causal and is_causal, dt)
+    if tensor_layout == "NHD":
+        o = o.transpose(-2, -3)
+    nq, nk = pr["map"].shape[-2:]
+    B = q.shape[0]
+    denom = (nk * nq * B * H) if not is_causal else ((nk + 2) // 2 * nq * B * H)   # core.py:162-167
+    sparsity = 1.0 - float(pr["valid"].float().sum()) / denom
+    out = (o, sparsity) if return_sparsity else o
+    if return_parts:
+        pr.update(v8=v8, v_scale=vs, km=km)
+        return out, pr
+    return out
+
+
+def block_sparse_sage2_attn(q, k, v, mask_id, scale=None, smooth_k=True, pvthreshd=50, tensor_layout="HND",
+                            return_sparsity=False, blockwise=True, return_parts=False):
+    """spas_sage_attn/core.py:171-233."""
+    q, k, v, dt = _prologue(q, k, v, tensor_layout)
+    B, H, N, D = q.shape
+    assert D in (64, 128)
+    km = k_mean(k) if smooth_k else None
+    dummy = torch.zeros(H)
+    _, _, q8, qs = pool_sim_quant(q, None, BLKQ, dummy, want_pool=False)
+    _, _, k8, ks = pool_sim_quant(k, km, BLKK, dummy, want_pool=False)
+    assert mask_id.dim() == 4
+    fmap = mask_id != 0
+    lut, valid = block_map_to_lut(fmap)
+    sm_scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    pv = hyperparameter_check(pvthreshd, H)
+    v8, vs = quant_v(v)
+    if blockwise:
+        o, _ = attention_blockwise(q8, qs, k8, ks, v8, vs, fmap, sm_scale, pv, False, dt)
+    else:
+        o = attention_dense_masked(q8, qs, k8, ks, v8, vs, fmap, sm_scale, False, dt)
+    if tensor_layout == "NHD":
+        o = o.transpose(-2, -3)
+    nq, nk = fmap.shape[-2:]
+    sparsity = 1.0 - float(valid.float().sum()) / ((nk + 2) // 2 * nq * B * H)     # core.py:229-231
+    out = (o, sparsity) if return_sparsity else o
+    if return_parts:
+        return out, dict(map=fmap, lut=lut, valid=valid, q_int8=q8, q_scale=qs, k_int8=k8, k_scale=ks,
+                         v8=v8, v_scale=vs, km=km)
+    return out
