@@ -1,0 +1,107 @@
+/*
+ * sparge_b200 -- C ABI of the B200 (sm_100a) block-sparse quantised attention path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, returns an int status
+ * (SPARGE_OK == 0), allocates nothing and keeps no global state unless its comment says so.
+ * All tensors are contiguous, "HND" layout: [B, H, N, D] with D in {64, 128}.
+ * 16-bit element type codes: SPARGE_F16 = 0, SPARGE_BF16 = 1.
+ * Block geometry is fixed: 128 query rows x 64 key rows per sparsity block
+ *   nq = ceil(N / 128), nk = ceil(N / 64), N_pad = nq * 128.
+ *
+ * Reference citations are path:line in the thu-ml/SpargeAttn source tree.
+ */
+#ifndef SPARGE_B200_H_
+#define SPARGE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* sparge_stream_t; /* a cudaStream_t */
+
+enum {
+  SPARGE_OK = 0,
+  SPARGE_ERR_INVALID_ARG = 1, /* bad head_dim / dtype code / sizes: maps to ValueError            */
+  SPARGE_ERR_NULL = 2,        /* a required pointer is NULL: maps to RuntimeError                  */
+  SPARGE_ERR_CUDA = 3,        /* a CUDA runtime / driver call failed: maps to RuntimeError         */
+  SPARGE_ERR_TOO_LARGE = 4,   /* a size exceeds what the kernel supports: maps to ValueError       */
+  SPARGE_ERR_UNSUPPORTED = 5  /* valid request that this build does not implement                  */
+};
+enum { SPARGE_F16 = 0, SPARGE_BF16 = 1 };
+
+/* Device-side status word values written by sparge_attn_fwd when a bounded wait expires. */
+enum { SPARGE_DEV_OK = 0, SPARGE_DEV_TIMEOUT_PRODUCER = 1, SPARGE_DEV_TIMEOUT_MMA = 2, SPARGE_DEV_TIMEOUT_SOFTMAX = 3 };
+
+const char* sparge_strerror(int status);
+int sparge_abi_version(void);
+
+/* Mean of K over tokens, in K's own 16-bit type.
+ * Replaces `km = k.mean(dim=-2, keepdim=True)` (spas_sage_attn/core.py:119-120).
+ *   k [B,H,N,D] -> km [B,H,D].  scratch: sparge_k_mean_scratch_bytes() bytes of device memory,
+ *   contents need no initialisation. */
+size_t sparge_k_mean_scratch_bytes(int B, int H, int N, int D);
+int sparge_k_mean(const void* k, void* km, void* scratch, int B, int H, int N, int D, int dtype,
+                  sparge_stream_t stream);
+
+/* Per-block pooling + cosine self-similarity + per-block INT8 quantisation in one pass.
+ * Replaces triton_bmm_pool_sim_simmean_fuse_quant (spas_sage_attn/utils.py:161-214, wrapper
+ * :270-280) and, with simthreshd1 == NULL, the quantiser-only qk_quantize (utils.py:89-159,
+ * wrappers :255-268).
+ *   x [B,H,N,D]; km [B,H,D] or NULL (subtracted in the 16-bit type before everything else);
+ *   block = 128 for Q, 64 for K; nb = ceil(N / block).
+ *   outputs: pool [B,H,nb,D] (same 16-bit type), sim [B,H,nb] (uint8 0/1), x_int8 [B,H,N,D],
+ *   scale [B,H,nb] fp32.  pool/sim may be NULL when simthreshd1 is NULL. */
+int sparge_pool_quant(const void* x, const void* km, const float* simthreshd1, void* pool, uint8_t* sim,
+                      int8_t* x_int8, float* scale, int B, int H, int N, int D, int block, int dtype,
+                      sparge_stream_t stream);
+
+/* Pooled-score map -> row softmax -> stable top-k (or cdf) selection -> forced blocks -> LUT.
+ * Replaces the torch/Triton chain of get_block_map_meansim_fuse_quant
+ * (spas_sage_attn/utils.py:386-420: bmm, masked fills, softmax, sort, cumsum, fill_block_map,
+ * causal mask, attention sink, block_map_lut_triton).
+ *   pq [B,H,nq,D], pk [B,H,nk,D] (16-bit), sim_q [B,H,nq], sim_k [B,H,nk] (uint8),
+ *   topk [H] fp32 or NULL, cdfthreshd [H] fp32 or NULL (exactly one non-NULL),
+ *   outputs: mask [B,H,nq,nk] uint8 (may be NULL), lut [B,H,nq,nk] int32 (first entry absolute,
+ *   then gaps, zero tail), valid [B,H,nq] int32.  Ties are broken towards the lower block index. */
+int sparge_select(const void* pq, const void* pk, const uint8_t* sim_q, const uint8_t* sim_k, const float* topk,
+                  const float* cdfthreshd, uint8_t* mask, int32_t* lut, int32_t* valid, int B, int H, int nq,
+                  int nk, int D, int dtype, int is_causal, int attention_sink, sparge_stream_t stream);
+
+/* User block mask -> LUT.  Replaces block_map_lut_triton / triton_block_map_to_lut_kernel
+ * (spas_sage_attn/utils.py:54-87).  mask [B,H,nq,nk] with elem_size in {1,2,4,8} bytes, any
+ * non-zero bit pattern counts as live. */
+int sparge_mask_to_lut(const void* mask, int elem_size, int32_t* lut, int32_t* valid, int B, int H, int nq, int nk,
+                       sparge_stream_t stream);
+
+/* Per-channel FP8 (e4m3) quantisation of V with scale_max 2.25.
+ * Replaces the fp16 cast (spas_sage_attn/core.py:115-117), transpose_pad_permute_cuda
+ * (csrc/fused/fused.cu:193-267) and scale_fuse_quant_cuda (fused.cu:269-344).
+ *   v [B,H,N,D] (16-bit; bf16 is rounded to fp16 first, as the reference does)
+ *   -> v8 [B,H,N_pad,D] e4m3 bytes, token-major, rows >= N zero; v_scale [B,H,D] fp32.
+ *   The reference's [B,H,D,N_pad] transposition and 16-token permutation are layout artefacts
+ *   of its mma.sync operand registers and are not reproduced. */
+int sparge_quant_v(const void* v, uint8_t* v8, float* v_scale, int B, int H, int N, int D, int dtype,
+                   sparge_stream_t stream);
+
+/* LUT-driven block-sparse attention: INT8 QK^T and FP8 PV on tcgen05 tensor cores.
+ * Replaces qk_int8_sv_f8_accum_f16_block_sparse_attn_inst_buf_fuse_v_scale_with_pv_threshold
+ * (csrc/qattn/qk_int_sv_f8_cuda_sm89.cu:392-585, kernel qk_int_sv_f8_cuda_sm89.cuh:42-755,
+ * declared at csrc/qattn/attn_cuda.h:19-123) with tensor_layout = HND, qk_quant_gran = per block.
+ *   q_int8, k_int8 [B,H,N,D]; v8 [B,H,N_pad,D]; o [B,H,N,D] (out_dtype); lut/valid as above;
+ *   pvthreshd [H] fp32 or NULL (NULL = never skip a PV block); q_scale [B,H,nq]; k_scale [B,H,nk];
+ *   v_scale [B,H,D]; dev_status: one int32 in device memory, or NULL. It is written only when a
+ *   bounded wait inside the kernel expires (SPARGE_DEV_*), never cleared.
+ *   is_causal != 0 masks key > query at token level.  Query rows whose block row has no live
+ *   block are written as zeros (the reference leaves them uninitialised). */
+int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o, const int32_t* lut,
+                    const int32_t* valid, const float* pvthreshd, const float* q_scale, const float* k_scale,
+                    const float* v_scale, int32_t* dev_status, int B, int H, int N, int D, int out_dtype,
+                    int is_causal, float sm_scale, sparge_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARGE_B200_H_ */

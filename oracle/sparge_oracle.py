@@ -62,20 +62,19 @@ def precision_metric(a: torch.Tensor, b: torch.Tensor) -> dict:
 
 
 def e4m3_round(x: torch.Tensor) -> torch.Tensor:
-    """fp32 -> e4m3 value (returned as fp32), round-to-nearest-even, saturating to +-448.
-
-    Follows `cvt.rn.satfinite.e4m3x2.f32` as used at csrc/numeric_conversion.cuh:48-63.  Written
-    out by hand because torch's CPU float8 cast does not saturate."""
+    """fp32 -> e4m3 value (returned as fp32): one round-to-nearest-even, saturating to +-448, as
+    `cvt.rn.satfinite.e4m3x2.f32` does (csrc/numeric_conversion.cuh:48-63; checked exhaustively on a
+    B200 for every fp32 in [2^-12, 512)).  Written out by hand because torch's CPU float8 cast does
+    not saturate."""
     x = x.to(torch.float32)
-    s = torch.sign(x)
     a = x.abs().clamp(max=448.0)
     # exponent of the e4m3 bucket: normal numbers have 3 mantissa bits, subnormals a fixed 2^-9 step
-    e = torch.floor(torch.log2(torch.where(a > 0, a, torch.ones_like(a))))
-    e = e.clamp(min=-6.0)
+    _, ex = torch.frexp(torch.where(a > 0, a, torch.ones_like(a)))     # a = mant * 2^ex, mant in [0.5, 1)
+    e = (ex - 1).to(torch.float32).clamp(min=-6.0)
     step = torch.exp2(e - 3.0)
     q = torch.round(a / step) * step          # torch.round is half-to-even; a/step is exact (power of two)
     q = q.clamp(max=448.0)
-    return torch.where(a > 0, s * q, torch.zeros_like(a) * s)
+    return torch.copysign(torch.where(a > 0, q, torch.zeros_like(a)), x)   # keeps the sign of -0 and of underflow
 
 
 def e4m3_bits(x: torch.Tensor) -> torch.Tensor:
@@ -253,7 +252,7 @@ def quant_v(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     v16 = v.to(torch.float16).float()
     amax = v16.abs().amax(dim=-2)                                     # [B,H,D]
     v_scale = amax / V_SCALE_MAX
-    r = V_SCALE_MAX / amax
+    r = torch.full_like(amax, V_SCALE_MAX) / amax                     # tensor / tensor: one IEEE division
     r = torch.where(amax > 0, r, torch.zeros_like(r))                 # all-zero channel: emit zeros, not NaN
     v8 = e4m3_round(v16 * r.unsqueeze(-2))
     npad = (N + 127) // 128 * 128

@@ -1,0 +1,187 @@
+"""Public operator API: the five functions of the reference's spas_sage_attn/core.py with the same
+names, signatures, defaults, assertions and return values, served by the sm_100a kernels.
+
+Differences from the reference, all deliberate:
+  * work is queued on PyTorch's current stream (the reference launches on the legacy default
+    stream, csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:780);
+  * V is consumed in its 16-bit input type and rounded to fp16 inside the quantiser instead of
+    being cast by torch first (same values, two fewer passes over V);
+  * `smooth_k=False` works (the reference raises NameError: `km` is undefined, core.py:119-128);
+  * query rows whose block row has no live block are zeros, not uninitialised memory;
+  * an all-zero V channel yields zeros instead of NaN.
+"""
+import torch
+
+from . import ops
+
+# The reference's Sage2 entry points pass the literal False in the kernel's is_causal slot
+# (spas_sage_attn/core.py:154-158, :221-225): causality is enforced per block by the predictor
+# only, and rows inside a diagonal block still see later keys of that block.  False keeps that
+# behaviour; True additionally masks key > query inside the kernel.
+SAGE2_TOKEN_LEVEL_CAUSAL = False
+
+
+def hyperparameter_check(hyper, H, device):
+    """spas_sage_attn/utils.py:38-50."""
+    if type(hyper) == float or type(hyper) == int:
+        hyper = torch.full((H,), float(hyper), device=device)
+    elif isinstance(hyper, torch.Tensor):
+        assert len(hyper.shape) <= 1, "Hyperparameter tensor must be 1D"
+        if len(hyper.shape) == 0:
+            hyper = torch.full((H,), hyper.item(), device=device)
+        assert hyper.numel() == H, f"Hyperparameter tensor must have {H} elements, but has {hyper.numel()}"
+        hyper = hyper.to(device)
+    else:
+        print(hyper)
+        raise ValueError("Hyperparameter must be a float or a tensor")
+    return hyper.to(torch.float32).contiguous()
+
+
+def _prologue(q, k, v, tensor_layout):
+    """spas_sage_attn/core.py:107-117."""
+    assert tensor_layout in ['HND', 'NHD']
+    if tensor_layout == 'NHD':
+        q, k, v = (t.transpose(-2, -3) for t in (q, k, v))
+    assert q.size(-2) >= 128, "seq_len should be not less than 128."
+    torch.cuda.set_device(v.device)
+    dtype = q.dtype
+    if dtype == torch.float32 or dtype == torch.float16:
+        q, k = q.contiguous().to(torch.float16), k.contiguous().to(torch.float16)
+    else:
+        q, k = q.contiguous().to(torch.bfloat16), k.contiguous().to(torch.bfloat16)
+    v = v.contiguous()
+    if v.dtype not in (torch.float16, torch.bfloat16):
+        v = v.to(torch.float16)
+    return q, k, v
+
+
+def get_block_map_meansim_fuse_quant(q, k, km=None, is_causal=False, BLKQ=128, BLKK=64, simthreshd1=0.1,
+                                     cdfthreshd=0.9, topk=None, is_sparse=True, return_lut=False,
+                                     attention_sink=False):
+    """spas_sage_attn/utils.py:371-421."""
+    assert (cdfthreshd is None and topk is not None) \
+        or (cdfthreshd is not None and topk is None), "Only one of cdfthreshd and topk can be set."
+    assert BLKQ == 128 and BLKK == 64, "this build fixes the sparsity block at 128 x 64"
+    Headnum = q.size(1)
+    simthreshd1 = hyperparameter_check(simthreshd1, Headnum, q.device)
+    if cdfthreshd is not None:
+        cdfthreshd = hyperparameter_check(cdfthreshd, Headnum, q.device)
+    if topk is not None:
+        topk = hyperparameter_check(topk, Headnum, q.device)
+    pooled_q, sim_q, q_int8, q_scale = ops.pool_sim_quant(q, None, BLKQ, simthreshd1)
+    pooled_k, sim_k, k_int8, k_scale = ops.pool_sim_quant(k, km, BLKK, simthreshd1)
+    lut, valid_block_num, final_map = ops.select_blocks(pooled_q, pooled_k, sim_q, sim_k, topk, cdfthreshd, is_causal,
+                                                        attention_sink, want_mask=not return_lut)
+    if not return_lut:
+        return final_map.bool(), q_int8, q_scale, k_int8, k_scale
+    return lut, valid_block_num, q_int8, q_scale, k_int8, k_scale
+
+
+def get_vanilla_qk_quant(q, k, km=None, BLKQ=128, BLKK=64):
+    """spas_sage_attn/utils.py:265-268."""
+    _, _, q_int8, q_scale = ops.pool_sim_quant(q, None, BLKQ, None)
+    _, _, k_int8, k_scale = ops.pool_sim_quant(k, km, BLKK, None)
+    return q_int8, q_scale, k_int8, k_scale
+
+
+def block_map_lut_triton(block_map):
+    """spas_sage_attn/utils.py:76-87 (name kept for callers; nothing here uses Triton)."""
+    return ops.mask_to_lut(block_map)
+
+
+def _sparsity(valid_block_num, lut, causal_denominator):
+    """spas_sage_attn/core.py:162-167, :229-231."""
+    if not causal_denominator:
+        denom = lut.size(3) * lut.size(2) * lut.size(0) * lut.size(1)
+    else:
+        denom = (lut.size(3) + 2) // 2 * lut.size(2) * lut.size(0) * lut.size(1)
+    return (1 - (valid_block_num.float().sum()) / denom).item()
+
+
+def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, topk, pvthreshd, attention_sink,
+                       tensor_layout, return_sparsity, kernel_causal):
+    q, k, v = _prologue(q, k, v, tensor_layout)
+    km = ops.k_mean(k) if smooth_k else None
+    headdim = q.size(-1)
+    assert headdim in [64, 128], "headdim should be in [64, 128]. For other headdim, you can use padding and specify the softmax scale."
+    lut, valid_block_num, q_int8, q_scale, k_int8, k_scale = get_block_map_meansim_fuse_quant(
+        q, k, km, is_causal=is_causal, simthreshd1=simthreshd1, cdfthreshd=cdfthreshd, topk=topk, return_lut=True,
+        attention_sink=attention_sink, BLKQ=128, BLKK=64)
+    if scale is None:
+        scale = 1.0 / (headdim ** 0.5)
+    pvthreshd = hyperparameter_check(pvthreshd, q.size(-3), q.device)
+    v_fp8, v_scale = ops.quant_v(v)
+    o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale,
+                     kernel_causal, q.dtype)
+    if tensor_layout == 'NHD':
+        o = o.transpose(-2, -3)
+    if return_sparsity:
+        return o, _sparsity(valid_block_num, lut, is_causal is not False)
+    return o
+
+
+@torch.compiler.disable
+def spas_sage2_attn_meansim_cuda(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, smooth_k=True,
+                                 simthreshd1=0.6, cdfthreshd=0.98, pvthreshd=50, attention_sink=False,
+                                 tensor_layout="HND", output_dtype=torch.float16, return_sparsity=False):
+    """spas_sage_attn/core.py:39-103 -- cdf-threshold selection, INT8 QK / FP8 PV."""
+    return _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, None, pvthreshd,
+                              attention_sink, tensor_layout, return_sparsity,
+                              bool(is_causal) and SAGE2_TOKEN_LEVEL_CAUSAL)
+
+
+@torch.compiler.disable
+def spas_sage2_attn_meansim_topk_cuda(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None,
+                                      smooth_k=True, simthreshd1=-0.1, cdfthreshd=None, topk=0.5, pvthreshd=50,
+                                      attention_sink=False, tensor_layout="HND", output_dtype=torch.float16,
+                                      return_sparsity=False):
+    """spas_sage_attn/core.py:105-169 -- top-k selection, INT8 QK / FP8 PV."""
+    return _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, topk, pvthreshd,
+                              attention_sink, tensor_layout, return_sparsity,
+                              bool(is_causal) and SAGE2_TOKEN_LEVEL_CAUSAL)
+
+
+@torch.compiler.disable
+def block_sparse_sage2_attn_cuda(q, k, v, mask_id=None, dropout_p=0.0, scale=None, smooth_k=True, pvthreshd=50,
+                                 attention_sink=False, tensor_layout="HND", output_dtype=torch.float16,
+                                 return_sparsity=False):
+    """spas_sage_attn/core.py:171-233 -- attention under a user-supplied 128x64 block mask."""
+    q, k, v = _prologue(q, k, v, tensor_layout)
+    km = ops.k_mean(k) if smooth_k else None
+    headdim = q.size(-1)
+    q_int8, q_scale, k_int8, k_scale = get_vanilla_qk_quant(q, k, km, 128, 64)
+    assert mask_id is not None, "mask_id is required"
+    lut, valid_block_num = block_map_lut_triton(block_map=mask_id)
+    if scale is None:
+        scale = 1.0 / (headdim ** 0.5)
+    assert headdim in [64, 128], "headdim should be in [64, 128]. For other headdim, you can use padding and specify the softmax scale."
+    pvthreshd = hyperparameter_check(pvthreshd, q.size(-3), q.device)
+    v_fp8, v_scale = ops.quant_v(v)
+    o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale, False,
+                     q.dtype)
+    if tensor_layout == 'NHD':
+        o = o.transpose(-2, -3)
+    if return_sparsity:
+        return o, _sparsity(valid_block_num, lut, True)   # core.py:229-231 always uses the causal denominator
+    return o
+
+
+@torch.compiler.disable
+def spas_sage_attn_meansim_cuda(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, smooth_k=True,
+                                simthreshd1=0.6, cdfthreshd=0.98, pvthreshd=50, attention_sink=False,
+                                tensor_layout="HND", output_dtype=torch.float16, return_sparsity=False):
+    """spas_sage_attn/core.py:235-276 -- Sage1 signature (cdf selection).  The reference runs an
+    fp16-PV mma.sync kernel here and forwards is_causal to it; this build serves it from the same
+    FP8-PV tcgen05 kernel with token-level causal masking."""
+    return _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, None, pvthreshd,
+                              attention_sink, tensor_layout, return_sparsity, bool(is_causal))
+
+
+@torch.compiler.disable
+def spas_sage_attn_meansim_topk_cuda(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None,
+                                     smooth_k=True, simthreshd1=-0.1, cdfthreshd=None, topk=0.5, pvthreshd=50,
+                                     attention_sink=False, tensor_layout="HND", output_dtype=torch.float16,
+                                     return_sparsity=False):
+    """spas_sage_attn/core.py:278-319 -- Sage1 signature (top-k selection), token-level causal."""
+    return _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, topk, pvthreshd,
+                              attention_sink, tensor_layout, return_sparsity, bool(is_causal))

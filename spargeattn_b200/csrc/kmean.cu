@@ -1,0 +1,78 @@
+// Mean of K over the token axis, computed with fp64 accumulation so that the result does not
+// depend on the reduction order, then rounded fp64 -> fp32 -> 16-bit.
+// Replaces `k.mean(dim=-2, keepdim=True)` at spas_sage_attn/core.py:119-120.
+#include "common.cuh"
+
+namespace sparge {
+
+constexpr int kMeanRowsPerCta = 512;
+
+// grid (chunks, B*H), 256 threads. Each thread owns 8 channels of every (256 / (D/8))-th row.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) kmean_partial_kernel(const T* __restrict__ k, double* __restrict__ part, int N) {
+  constexpr int TPR = D / 8;        // threads per row
+  constexpr int RPP = 256 / TPR;    // rows per pass
+  __shared__ double red[RPP][D];
+  const int tid = threadIdx.x, cg = tid % TPR, r0 = tid / TPR;
+  const int chunk = blockIdx.x, bh = blockIdx.y, chunks = gridDim.x;
+  const int row_begin = chunk * kMeanRowsPerCta;
+  const int row_end = min(N, row_begin + kMeanRowsPerCta);
+  const T* base = k + (size_t)bh * N * D;
+  double acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.0;
+  for (int row = row_begin + r0; row < row_end; row += RPP) {
+    Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * D + cg * 8);
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] += (double)Elem<T>::to_float(p.v[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) red[r0][cg * 8 + i] = acc[i];
+  __syncthreads();
+  if (tid < D) {
+    double s = 0.0;
+#pragma unroll 4
+    for (int r = 0; r < RPP; r++) s += red[r][tid];
+    part[((size_t)bh * chunks + chunk) * D + tid] = s;
+  }
+}
+
+// grid (B*H), D threads.
+template <typename T, int D>
+__global__ void kmean_final_kernel(const double* __restrict__ part, T* __restrict__ km, int N, int chunks) {
+  const int bh = blockIdx.x, d = threadIdx.x;
+  double s = 0.0;
+  for (int c = 0; c < chunks; c++) s += part[((size_t)bh * chunks + c) * D + d];
+  km[(size_t)bh * D + d] = Elem<T>::from_float((float)(s / (double)N));
+}
+
+template <typename T, int D>
+static int launch_kmean(const void* k, void* km, void* scratch, int BH, int N, cudaStream_t st) {
+  const int chunks = (N + kMeanRowsPerCta - 1) / kMeanRowsPerCta;
+  kmean_partial_kernel<T, D><<<dim3(chunks, BH), 256, 0, st>>>((const T*)k, (double*)scratch, N);
+  kmean_final_kernel<T, D><<<BH, D, 0, st>>>((const double*)scratch, (T*)km, N, chunks);
+  return launch_status();
+}
+
+}  // namespace sparge
+
+extern "C" size_t sparge_k_mean_scratch_bytes(int B, int H, int N, int D) {
+  if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
+  const size_t chunks = ((size_t)N + sparge::kMeanRowsPerCta - 1) / sparge::kMeanRowsPerCta;
+  return (size_t)B * H * chunks * D * sizeof(double);
+}
+
+extern "C" int sparge_k_mean(const void* k, void* km, void* scratch, int B, int H, int N, int D, int dtype,
+                             sparge_stream_t stream) {
+  using namespace sparge;
+  if (!k || !km || !scratch) return SPARGE_ERR_NULL;
+  if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (dtype != SPARGE_F16 && dtype != SPARGE_BF16))
+    return SPARGE_ERR_INVALID_ARG;
+  if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int BH = B * H;
+  if (dtype == SPARGE_F16)
+    return D == 64 ? launch_kmean<__half, 64>(k, km, scratch, BH, N, st) : launch_kmean<__half, 128>(k, km, scratch, BH, N, st);
+  return D == 64 ? launch_kmean<__nv_bfloat16, 64>(k, km, scratch, BH, N, st)
+                 : launch_kmean<__nv_bfloat16, 128>(k, km, scratch, BH, N, st);
+}

@@ -1,0 +1,113 @@
+// Per-channel FP8 (e4m3) quantisation of V: v16 = fp16(v); amax over tokens per (b,h,d);
+// v_scale = amax / 2.25; v8 = e4m3_rn_satfinite(v16 * (2.25 / amax)).
+// Replaces the fp16 cast at spas_sage_attn/core.py:115-117, TransposePadPermuteKernel
+// (csrc/fused/fused.cu:26-77) and MeanScaleKernel (fused.cu:80-191).
+// Output is token-major [B,H,N_pad,D] with zero rows beyond N: the tcgen05 PV MMA takes V as an
+// MN-major B operand straight from that layout, so no transposed copy is made.
+// An all-zero channel is emitted as zeros (the reference produces NaN there).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace sparge {
+
+constexpr int kVRowsPerCta = 256;
+constexpr float kVScaleMax = 2.25f;   // spas_sage_attn/core.py:151
+
+template <typename T>
+__device__ __forceinline__ float to_f16_value(T v);
+template <>
+__device__ __forceinline__ float to_f16_value<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f16_value<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __half2float(__float2half_rn(__bfloat162float(v)));
+}
+
+// grid (chunks, B*H), 256 threads. amax accumulates as the bit pattern of a non-negative float.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) v_amax_kernel(const T* __restrict__ v, unsigned int* __restrict__ amax_bits, int N) {
+  constexpr int TPR = D / 8, RPP = 256 / TPR;
+  __shared__ float red[RPP][D];
+  const int tid = threadIdx.x, cg = tid % TPR, r0 = tid / TPR;
+  const int bh = blockIdx.y;
+  const int row_begin = blockIdx.x * kVRowsPerCta, row_end = min(N, row_begin + kVRowsPerCta);
+  const T* base = v + (size_t)bh * N * D;
+  float mx[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) mx[i] = 0.f;
+  for (int row = row_begin + r0; row < row_end; row += RPP) {
+    Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * D + cg * 8);
+#pragma unroll
+    for (int i = 0; i < 8; i++) mx[i] = fmaxf(mx[i], fabsf(to_f16_value<T>(p.v[i])));
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) red[r0][cg * 8 + i] = mx[i];
+  __syncthreads();
+  if (tid < D) {
+    float m = 0.f;
+#pragma unroll 4
+    for (int r = 0; r < RPP; r++) m = fmaxf(m, red[r][tid]);
+    atomicMax(amax_bits + (size_t)bh * D + tid, __float_as_uint(m));
+  }
+}
+
+// grid (ceil(N_pad / rows), B*H), 256 threads.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) v_quant_kernel(const T* __restrict__ v, const float* __restrict__ amax,
+                                                      uint8_t* __restrict__ v8, int N, int N_pad) {
+  constexpr int TPR = D / 8, RPP = 256 / TPR;
+  const int tid = threadIdx.x, cg = tid % TPR, r0 = tid / TPR;
+  const int bh = blockIdx.y;
+  const int row_begin = blockIdx.x * kVRowsPerCta, row_end = min(N_pad, row_begin + kVRowsPerCta);
+  float r[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const float a = amax[(size_t)bh * D + cg * 8 + i];
+    r[i] = a > 0.f ? __fdiv_rn(kVScaleMax, a) : 0.f;
+  }
+  const T* base = v + (size_t)bh * N * D;
+  uint8_t* out = v8 + (size_t)bh * N_pad * D;
+  for (int row = row_begin + r0; row < row_end; row += RPP) {
+    uint2 w = make_uint2(0u, 0u);
+    if (row < N) {
+      Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * D + cg * 8);
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) f[i] = __fmul_rn(to_f16_value<T>(p.v[i]), r[i]);
+      w.x = cvt_e4m3x4(f[0], f[1], f[2], f[3]);
+      w.y = cvt_e4m3x4(f[4], f[5], f[6], f[7]);
+    }
+    *reinterpret_cast<uint2*>(out + (size_t)row * D + cg * 8) = w;
+  }
+}
+
+__global__ void v_scale_final_kernel(float* __restrict__ v_scale, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) v_scale[i] = __fdiv_rn(v_scale[i], kVScaleMax);
+}
+
+template <typename T, int D>
+static int launch_quant_v(const void* v, uint8_t* v8, float* v_scale, int BH, int N, cudaStream_t st) {
+  const int N_pad = (N + 127) / 128 * 128;
+  if (cudaMemsetAsync(v_scale, 0, (size_t)BH * D * sizeof(float), st) != cudaSuccess) return SPARGE_ERR_CUDA;
+  v_amax_kernel<T, D><<<dim3((N + kVRowsPerCta - 1) / kVRowsPerCta, BH), 256, 0, st>>>((const T*)v, (unsigned int*)v_scale, N);
+  v_quant_kernel<T, D><<<dim3((N_pad + kVRowsPerCta - 1) / kVRowsPerCta, BH), 256, 0, st>>>((const T*)v, v_scale, v8, N, N_pad);
+  v_scale_final_kernel<<<(BH * D + 255) / 256, 256, 0, st>>>(v_scale, BH * D);
+  return launch_status();
+}
+
+}  // namespace sparge
+
+extern "C" int sparge_quant_v(const void* v, uint8_t* v8, float* v_scale, int B, int H, int N, int D, int dtype,
+                              sparge_stream_t stream) {
+  using namespace sparge;
+  if (!v || !v8 || !v_scale) return SPARGE_ERR_NULL;
+  if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (dtype != SPARGE_F16 && dtype != SPARGE_BF16))
+    return SPARGE_ERR_INVALID_ARG;
+  if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int BH = B * H;
+  if (dtype == SPARGE_F16)
+    return D == 64 ? launch_quant_v<__half, 64>(v, v8, v_scale, BH, N, st) : launch_quant_v<__half, 128>(v, v8, v_scale, BH, N, st);
+  return D == 64 ? launch_quant_v<__nv_bfloat16, 64>(v, v8, v_scale, BH, N, st)
+                 : launch_quant_v<__nv_bfloat16, 128>(v, v8, v_scale, BH, N, st);
+}

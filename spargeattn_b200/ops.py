@@ -1,0 +1,135 @@
+"""Tensor-level wrappers over the C ABI: allocate outputs with torch, pass raw pointers and the
+current CUDA stream.  These mirror the helper functions of the reference's
+spas_sage_attn/utils.py (get_pool_sim_triton_simmean_fuse_quant :270-280, get_quant :255-263,
+block_map_lut_triton :76-87) and the `_fused` / `_qattn` extension calls in core.py:143-158."""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi
+
+BLKQ, BLKK = 128, 64
+_status_words = {}
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return _cabi.F16
+    if t.dtype == torch.bfloat16:
+        return _cabi.BF16
+    raise ValueError(f"expected a float16 or bfloat16 tensor, got {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("spargeattn_b200 runs on CUDA tensors only (no CPU path)")
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError("expected a contiguous tensor")
+
+
+def device_status_word(device) -> torch.Tensor:
+    """One int32 per device that sparge_attn_fwd writes when a bounded in-kernel wait expires."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return _status_words[key]
+
+
+def check_device_status(device=None) -> int:
+    """Synchronising read of the device status word; raises if a kernel reported a timeout."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    code = int(device_status_word(dev).item())
+    if code != 0:
+        raise RuntimeError(f"sparge_attn_fwd reported device status {code} (a bounded wait expired)")
+    return code
+
+
+def k_mean(k: torch.Tensor) -> torch.Tensor:
+    _need_cuda(k)
+    B, H, N, D = k.shape
+    km = torch.empty(B, H, 1, D, dtype=k.dtype, device=k.device)
+    nbytes = _cabi.lib.sparge_k_mean_scratch_bytes(B, H, N, D)
+    scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=k.device)
+    _cabi.check(_cabi.lib.sparge_k_mean(_ptr(k), _ptr(km), _ptr(scratch), B, H, N, D, _dt(k), _stream(k)), "sparge_k_mean")
+    return km
+
+
+def pool_sim_quant(x: torch.Tensor, km: Optional[torch.Tensor], block: int, simthreshd1: Optional[torch.Tensor]):
+    """Returns (pool, sim, x_int8, scale); pool and sim are None when simthreshd1 is None."""
+    _need_cuda(x, km, simthreshd1)
+    B, H, N, D = x.shape
+    nb = (N + block - 1) // block
+    x8 = torch.empty(B, H, N, D, dtype=torch.int8, device=x.device)
+    scale = torch.empty(B, H, nb, dtype=torch.float32, device=x.device)
+    pool = sim = None
+    if simthreshd1 is not None:
+        pool = torch.empty(B, H, nb, D, dtype=x.dtype, device=x.device)
+        sim = torch.empty(B, H, nb, dtype=torch.uint8, device=x.device)
+    _cabi.check(_cabi.lib.sparge_pool_quant(_ptr(x), _ptr(km), _ptr(simthreshd1), _ptr(pool), _ptr(sim), _ptr(x8),
+                                            _ptr(scale), B, H, N, D, block, _dt(x), _stream(x)), "sparge_pool_quant")
+    return pool, sim, x8, scale
+
+
+def select_blocks(pq, pk, sim_q, sim_k, topk: Optional[torch.Tensor], cdfthreshd: Optional[torch.Tensor],
+                  is_causal: bool, attention_sink: bool, want_mask: bool = False):
+    """Returns (lut, valid, mask-or-None)."""
+    _need_cuda(pq, pk, sim_q, sim_k, topk, cdfthreshd)
+    B, H, nq, D = pq.shape
+    nk = pk.shape[2]
+    lut = torch.empty(B, H, nq, nk, dtype=torch.int32, device=pq.device)
+    valid = torch.empty(B, H, nq, dtype=torch.int32, device=pq.device)
+    mask = torch.empty(B, H, nq, nk, dtype=torch.uint8, device=pq.device) if want_mask else None
+    _cabi.check(_cabi.lib.sparge_select(_ptr(pq), _ptr(pk), _ptr(sim_q), _ptr(sim_k), _ptr(topk), _ptr(cdfthreshd),
+                                        _ptr(mask), _ptr(lut), _ptr(valid), B, H, nq, nk, D, _dt(pq),
+                                        int(bool(is_causal)), int(bool(attention_sink)), _stream(pq)), "sparge_select")
+    return lut, valid, mask
+
+
+def mask_to_lut(block_map: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    assert block_map.dim() == 4
+    assert block_map.is_contiguous()
+    _need_cuda(block_map)
+    if block_map.dtype == torch.bool:
+        block_map = block_map.view(torch.uint8)
+    elif block_map.dtype.is_floating_point:
+        block_map = (block_map != 0).view(torch.uint8)   # -0.0 must count as false
+    B, H, nq, nk = block_map.shape
+    lut = torch.empty(B, H, nq, nk, dtype=torch.int32, device=block_map.device)
+    valid = torch.empty(B, H, nq, dtype=torch.int32, device=block_map.device)
+    _cabi.check(_cabi.lib.sparge_mask_to_lut(_ptr(block_map), block_map.element_size(), _ptr(lut), _ptr(valid), B, H,
+                                             nq, nk, _stream(block_map)), "sparge_mask_to_lut")
+    return lut, valid
+
+
+def quant_v(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """v [B,H,N,D] fp16/bf16 -> (v8 uint8 [B,H,N_pad,D] e4m3 bytes, v_scale [B,H,D])."""
+    _need_cuda(v)
+    B, H, N, D = v.shape
+    npad = (N + 127) // 128 * 128
+    v8 = torch.empty(B, H, npad, D, dtype=torch.uint8, device=v.device)
+    vs = torch.empty(B, H, D, dtype=torch.float32, device=v.device)
+    _cabi.check(_cabi.lib.sparge_quant_v(_ptr(v), _ptr(v8), _ptr(vs), B, H, N, D, _dt(v), _stream(v)), "sparge_quant_v")
+    return v8, vs
+
+
+def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale, k_scale, v_scale, sm_scale: float,
+             is_causal: bool, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(q8, k8, v8, lut, valid, pvthreshd, q_scale, k_scale, v_scale, out)
+    B, H, N, D = q8.shape
+    if out is None:
+        out = torch.empty(B, H, N, D, dtype=out_dtype, device=q8.device)
+    status = device_status_word(q8.device)
+    _cabi.check(_cabi.lib.sparge_attn_fwd(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
+                                          _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale), _ptr(status),
+                                          B, H, N, D, _dt(out), int(bool(is_causal)), float(sm_scale), _stream(q8)),
+                "sparge_attn_fwd")
+    return out
