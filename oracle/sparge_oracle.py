@@ -320,20 +320,21 @@ def attention_dense_masked(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_
     """Oracle A: fp32 softmax attention on the de-quantised operands with the 128x64 block map
     expanded to tokens (spas_sage_attn/utils.py:424-432).  No fp8 rounding of P, no PV skip.
     Also the CPU baseline that the benchmark times."""
-    B, H, N, D = q8.shape
+    B, H, N, D = q8.shape                                             # N: query rows given (a prefix is allowed)
+    NK = k8.shape[2]
     nq, nk = block_map.shape[-2:]
     qd = q8.float() * q_scale.repeat_interleave(BLKQ, dim=-1)[..., :N].unsqueeze(-1)
-    kd = k8.float() * k_scale.repeat_interleave(BLKK, dim=-1)[..., :N].unsqueeze(-1)
-    vd = v8[:, :, :N] * v_scale.unsqueeze(-2)
+    kd = k8.float() * k_scale.repeat_interleave(BLKK, dim=-1)[..., :NK].unsqueeze(-1)
+    vd = v8[:, :, :NK] * v_scale.unsqueeze(-2)
     o = torch.zeros(B, H, N, D, dtype=torch.float32)
     for r0 in range(0, N, q_chunk):
         r1 = min(r0 + q_chunk, N)
         assert r0 % BLKQ == 0
         bm = block_map[:, :, r0 // BLKQ:(r1 + BLKQ - 1) // BLKQ]
-        mask = block_map_to_mask(bm, r1 - r0, N)
+        mask = block_map_to_mask(bm, r1 - r0, NK)
         if token_causal:
             qi = torch.arange(r0, r1).view(-1, 1)
-            kj = torch.arange(N).view(1, -1)
+            kj = torch.arange(NK).view(1, -1)
             mask = mask & (kj <= qi)
         s = torch.matmul(qd[:, :, r0:r1], kd.transpose(-1, -2)) * sm_scale
         s = s.masked_fill(~mask, float("-inf"))
