@@ -1,0 +1,107 @@
+"""CPU tests: the oracle against fixtures produced by the reference's own preprocessing code
+(tests/golden/make_golden.py ran the reference's Triton kernels under the Triton interpreter),
+plus self-consistency of the oracle's pieces."""
+import glob
+import os
+
+import pytest
+import torch
+
+import sparge_oracle as O
+from make_golden import golden_inputs
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_predictor_*.pt")))
+
+
+def test_fixtures_present():
+    assert len(GOLDEN) >= 4
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+def test_oracle_matches_reference_fixture(path):
+    g = torch.load(path)
+    B, H, N, D, causal, topk, cdf, sim1, sink, seed = g["case"]
+    q, k = golden_inputs(B, H, N, D, seed)
+    pr = O.predictor(q, k, g["km"], causal, sim1, cdf, topk, sink)
+    assert torch.equal(pr["q_int8"], g["q_int8"]) and torch.equal(pr["k_int8"], g["k_int8"])
+    assert torch.equal(pr["q_scale"], g["q_scale"]) and torch.equal(pr["k_scale"], g["k_scale"])
+    assert torch.equal(pr["map"], g["map"])
+    assert torch.equal(pr["lut"], g["lut"]) and torch.equal(pr["valid"], g["valid"])
+    assert g["vanilla_equal"]          # the quantiser-only kernel agrees with the fused one in the reference
+    # the pinned (fp64) K mean agrees with torch's fp16 mean on these inputs
+    assert torch.equal(O.k_mean(k), g["km"])
+
+
+def _ref_block_map_lut(block_map):
+    """Reference semantics of the LUT in plain Python (spas_sage_attn/utils.py:54-74)."""
+    B, H, Q, K = block_map.shape
+    lut = torch.zeros(B, H, Q, K, dtype=torch.int32)
+    valid = torch.zeros(B, H, Q, dtype=torch.int32)
+    for b in range(B):
+        for h in range(H):
+            for q in range(Q):
+                n, prev = 0, 0
+                for i in range(K):
+                    if block_map[b, h, q, i]:
+                        lut[b, h, q, n] = i - prev
+                        n += 1
+                        prev = i
+                valid[b, h, q] = n
+    return lut, valid
+
+
+def test_lut_encoding():
+    g = torch.Generator().manual_seed(0)
+    m = torch.rand(2, 2, 5, 13, generator=g) < 0.4
+    m[0, 0, 0] = False
+    m[0, 0, 1] = True
+    lut, valid = O.block_map_to_lut(m)
+    rl, rv = _ref_block_map_lut(m)
+    assert torch.equal(lut, rl) and torch.equal(valid, rv)
+
+
+def test_e4m3_round_matches_torch_cast_in_range():
+    x = torch.cat([torch.randn(200000) * 40, torch.tensor([0.0, -0.0, 448.0, 1e-4, -1e-4, 2.0 ** -9, 1.5 * 2.0 ** -9])])
+    ref = x.clamp(-448, 448).to(torch.float8_e4m3fn).float()
+    got = O.e4m3_round(x)
+    assert torch.equal(got, ref) and torch.equal(torch.signbit(got), torch.signbit(ref))
+    assert O.e4m3_round(torch.tensor([1000.0, -1e9])).tolist() == [448.0, -448.0]
+
+
+def test_partial_blocks_are_never_self_similar():
+    """spas_sage_attn/utils.py:181-199: a trailing partial block is forced live for every row/column."""
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(1, 2, 600, 64, generator=g).bfloat16()
+    k = torch.randn(1, 2, 600, 64, generator=g).bfloat16()
+    pr = O.predictor(q, k, O.k_mean(k), topk=0.2)
+    assert pr["map"][..., -1, :].all() and pr["map"][..., :, -1].all()
+    assert not pr["sim_q"][..., -1].any() and not pr["sim_k"][..., -1].any()
+
+
+def test_topk_count_and_stability():
+    p = torch.tensor([[[[0.25, 0.25, 0.25, 0.25, 0.0, 0.0, 0.0, 0.0]]]]).bfloat16()
+    sim = torch.ones(1, 1, 1, dtype=torch.bool)
+    simk = torch.ones(1, 1, 8, dtype=torch.bool)
+    m = O.select_blocks(p, sim, simk, torch.tensor([0.25]), None, False, False)
+    assert m[0, 0, 0].tolist() == [True, True] + [False] * 6          # int(0.25 * 8) = 2, lowest indices win
+    m = O.select_blocks(p, sim, simk, torch.tensor([0.01]), None, False, False)
+    assert m.sum() == 1                                               # at least one block per row
+
+
+def test_blockwise_attention_close_to_dense_masked():
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(1, 2, 512, 64, generator=g).bfloat16() for _ in range(3))
+    o_b = O.spas_sage2_attn_meansim_topk(q, k, v, topk=0.5, blockwise=True)
+    o_d = O.spas_sage2_attn_meansim_topk(q, k, v, topk=0.5, blockwise=False)
+    m = O.precision_metric(o_b, o_d)
+    assert m["Cossim"] > 0.998 and m["L1"] < 0.06
+
+
+def test_sparsity_formulas():
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(1, 2, 1024, 64, generator=g).bfloat16() for _ in range(3))
+    _, sp = O.spas_sage2_attn_meansim_topk(q, k, v, topk=0.5, return_sparsity=True, blockwise=False)
+    assert abs(sp - 0.5) < 1e-6
+    mask = torch.ones(1, 2, 8, 16, dtype=torch.int32)
+    _, sp = O.block_sparse_sage2_attn(q, k, v, mask, return_sparsity=True, blockwise=False)
+    assert abs(sp - (1 - 16 * 8 * 2 / ((16 + 2) // 2 * 8 * 2))) < 1e-6     # core.py:229-231 denominator
