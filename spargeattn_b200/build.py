@@ -1,6 +1,6 @@
 """Builds libsparge_b200.so in-tree with nvcc for sm_100a (no other architecture is targeted).
 
-    python -m spargeattn_b200.build [--force] [--verbose]
+    python spargeattn_b200/build.py [--force] [--verbose]
 """
 import os
 import subprocess
