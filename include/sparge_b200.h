@@ -46,6 +46,26 @@ size_t sparge_k_mean_scratch_bytes(int B, int H, int N, int D);
 int sparge_k_mean(const void* k, void* km, void* scratch, int B, int H, int N, int D, int dtype,
                   sparge_stream_t stream);
 
+/* Allocation-free variant of sparge_k_mean. It has no counterpart in the reference.
+ *
+ * Who it is for: hosts that must not (or cannot) obtain device memory at call time -- a serving
+ * process whose framework has already claimed the whole GPU for its own pool, a plugin that is
+ * handed tensors but no allocator, or a latency-critical loop where cudaMalloc/cudaFree would stall
+ * the device.  The caller still passes the input and the output; only the scratch is supplied by the
+ * library, from a fixed array of SPARGE_K_MEAN_STATIC_MAX_BYTES that is part of the library image
+ * (each GPU that loads the library holds that much memory until the process exits).
+ *
+ *   - Requests needing more scratch than the array holds return SPARGE_ERR_TOO_LARGE:
+ *     sparge_k_mean_scratch_bytes(B,H,N,D) = B*H*ceil(N/512)*D*8 must be <= the maximum.
+ *   - The first call on each device looks up the array's device address (no allocation). Make that
+ *     first call outside any stream capture, with the intended device current.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left in it.
+ *     The kernels overwrite every element they later read, so no clearing is needed, but two calls
+ *     whose kernels can overlap on the GPU (different streams, no dependency) race on it: order them.
+ *   - Calls no cudaMalloc, cudaFree or other allocating routine.  Same results as sparge_k_mean. */
+#define SPARGE_K_MEAN_STATIC_MAX_BYTES (8u << 20)
+int sparge_k_mean_static(const void* k, void* km, int B, int H, int N, int D, int dtype, sparge_stream_t stream);
+
 /* Per-block pooling + cosine self-similarity + per-block INT8 quantisation in one pass.
  * Replaces triton_bmm_pool_sim_simmean_fuse_quant (spas_sage_attn/utils.py:161-214, wrapper
  * :270-280) and, with simthreshd1 == NULL, the quantiser-only qk_quantize (utils.py:89-159,

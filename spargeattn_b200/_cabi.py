@@ -1,7 +1,7 @@
 """ctypes binding of libsparge_b200.so (the C ABI declared in include/sparge_b200.h).
 
 There is no fallback: if the shared library has not been built, importing this module raises.
-Build it with `python -m spargeattn_b200.build`.
+Build it with `python spargeattn_b200/build.py`.
 """
 import ctypes
 import os
@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libsparge_b200.so")
 if not os.path.exists(LIB_PATH):
     raise ImportError(
         f"{LIB_PATH} is missing: the sm_100a CUDA library has not been built. "
-        "Run `python -m spargeattn_b200.build` (needs nvcc); there is no CPU or PyTorch fallback.")
+        "Run `python spargeattn_b200/build.py` (needs nvcc); there is no CPU or PyTorch fallback.")
 
 lib = ctypes.CDLL(LIB_PATH)
 
@@ -24,6 +24,7 @@ SIGNATURES = {
     "sparge_abi_version": (_i, []),
     "sparge_k_mean_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "sparge_k_mean": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "sparge_k_mean_static": (_i, [_p, _p, _i, _i, _i, _i, _i, _p]),
     "sparge_pool_quant": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "sparge_select": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "sparge_mask_to_lut": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p]),

@@ -1,11 +1,19 @@
 // Mean of K over the token axis, computed with fp64 accumulation so that the result does not
 // depend on the reduction order, then rounded fp64 -> fp32 -> 16-bit.
 // Replaces `k.mean(dim=-2, keepdim=True)` at spas_sage_attn/core.py:119-120.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace sparge {
 
 constexpr int kMeanRowsPerCta = 512;
+
+// Scratch of the allocation-free entry point: lives in the library image, one copy per GPU that
+// loads the library, for the life of the process. In host code this name is only a handle; the
+// device address is obtained with cudaGetSymbolAddress (once per device) and passed to the kernels.
+constexpr size_t kStaticScratchDoubles = SPARGE_K_MEAN_STATIC_MAX_BYTES / sizeof(double);
+static __device__ __align__(256) double g_kmean_static_scratch[kStaticScratchDoubles];
 
 // grid (chunks, B*H), 256 threads. Each thread owns 8 channels of every (256 / (D/8))-th row.
 template <typename T, int D>
@@ -75,4 +83,34 @@ extern "C" int sparge_k_mean(const void* k, void* km, void* scratch, int B, int 
     return D == 64 ? launch_kmean<__half, 64>(k, km, scratch, BH, N, st) : launch_kmean<__half, 128>(k, km, scratch, BH, N, st);
   return D == 64 ? launch_kmean<__nv_bfloat16, 64>(k, km, scratch, BH, N, st)
                  : launch_kmean<__nv_bfloat16, 128>(k, km, scratch, BH, N, st);
+}
+
+extern "C" int sparge_k_mean_static(const void* k, void* km, int B, int H, int N, int D, int dtype,
+                                    sparge_stream_t stream) {
+  using namespace sparge;
+  if (!k || !km) return SPARGE_ERR_NULL;
+  if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (dtype != SPARGE_F16 && dtype != SPARGE_BF16))
+    return SPARGE_ERR_INVALID_ARG;
+  if (sparge_k_mean_scratch_bytes(B, H, N, D) > (size_t)SPARGE_K_MEAN_STATIC_MAX_BYTES) return SPARGE_ERR_TOO_LARGE;
+
+  // Per-device set-up on the first call: resolve the device address of the static array with the
+  // calling thread's current device. Nothing is allocated here or later.
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static double* dev_ptr[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SPARGE_ERR_CUDA;
+  double* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_kmean_static_scratch) != cudaSuccess || p == nullptr) return SPARGE_ERR_CUDA;
+      dev_ptr[dev] = static_cast<double*>(p);
+    }
+    scratch = dev_ptr[dev];
+  }
+  // The partial sums fill every scratch element that the second kernel reads, so nothing needs
+  // clearing between calls.
+  return sparge_k_mean(k, km, scratch, B, H, N, D, dtype, stream);
 }
