@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--topk", type=float, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="device-resident arm only (for profiler runs)")
     return ap.parse_args()
 
 
@@ -221,6 +222,15 @@ def main():
     ops.check_device_status(dev)
     total_ops = dense_equiv_ops(B, H, N, D, causal) * world
     value = total_ops / (ms_step * 1e-3) / 1e12
+
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": ms_step, "quick": True,
+                              "config": config_dict(idx, w, topk, world)}))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     # ---- end-to-end arm: pinned host buffers in, host buffer out, copies inside the timed region
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
