@@ -37,6 +37,19 @@ def hyperparameter_check(hyper, H, device):
     return hyper.to(torch.float32).contiguous()
 
 
+# A PV block is skipped when every row's new maximum is at least pvthreshd (in log2 units) below
+# the running one (qk_int_sv_f8_cuda_sm89.cuh:353).  From 8.807 + 10 = 18.8 upward every probability
+# of such a block rounds to zero in e4m3 anyway, so with a scalar threshold this large the kernel
+# variant without the test produces the same output (the denominators differ by < 2^-30 relative).
+PV_SKIP_NEVER_FIRES_FROM = 30.0
+
+
+def _pv_threshold_tensor(pvthreshd, H, device):
+    if type(pvthreshd) in (int, float) and float(pvthreshd) >= PV_SKIP_NEVER_FIRES_FROM:
+        return None
+    return hyperparameter_check(pvthreshd, H, device)
+
+
 def _prologue(q, k, v, tensor_layout):
     """spas_sage_attn/core.py:107-117."""
     assert tensor_layout in ['HND', 'NHD']
@@ -109,7 +122,7 @@ def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthre
         attention_sink=attention_sink, BLKQ=128, BLKK=64)
     if scale is None:
         scale = 1.0 / (headdim ** 0.5)
-    pvthreshd = hyperparameter_check(pvthreshd, q.size(-3), q.device)
+    pvthreshd = _pv_threshold_tensor(pvthreshd, q.size(-3), q.device)
     v_fp8, v_scale = ops.quant_v(v)
     o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale,
                      kernel_causal, q.dtype)
@@ -155,7 +168,7 @@ def block_sparse_sage2_attn_cuda(q, k, v, mask_id=None, dropout_p=0.0, scale=Non
     if scale is None:
         scale = 1.0 / (headdim ** 0.5)
     assert headdim in [64, 128], "headdim should be in [64, 128]. For other headdim, you can use padding and specify the softmax scale."
-    pvthreshd = hyperparameter_check(pvthreshd, q.size(-3), q.device)
+    pvthreshd = _pv_threshold_tensor(pvthreshd, q.size(-3), q.device)
     v_fp8, v_scale = ops.quant_v(v)
     o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale, False,
                      q.dtype)

@@ -25,6 +25,15 @@ namespace sparge {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kFp8Offset = 8.807f;     // csrc/qattn/attn_utils.cuh:28-30: 2^8.807 = 448 = e4m3 max
 constexpr float kMaskValue = -5000000.0f;  // csrc/qattn/attn_utils.cuh:348-352
+constexpr uint32_t kMagicBits = 0x4B400000u;   // bit pattern of 12582912.0f = 1.5 * 2^23
+constexpr float kMagic = 12582912.0f;
+
+#ifdef SPARGE_EXP_TRACE
+#define TRACE(who, n, ev) do { if (blockIdx.x == 4 && blockIdx.y == 0 && (n) >= 8 && (n) < 24) \
+  reinterpret_cast<long long*>(dev_status + 16)[((who) * 16 + ((n) - 8)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define TRACE(who, n, ev) do {} while (0)
+#endif
 
 template <int D>
 struct AttnShape {
@@ -99,8 +108,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     }
     mbar_init(&bar_s_full[0], 1);
     mbar_init(&bar_s_full[1], 1);
-    mbar_init(&bar_p_ready[0], 128);
-    mbar_init(&bar_p_ready[1], 128);
+    mbar_init(&bar_p_ready[0], 4);    // one arrival per softmax warp
+    mbar_init(&bar_p_ready[1], 4);
     mbar_init(&bar_o_done, 1);
     mbar_init(&bar_delta[0], 4);
     mbar_init(&bar_delta[1], 4);
@@ -169,8 +178,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       bool ok = mbar_wait(&bar_q, 0);
       auto issue_pv = [&](int m) {
         const int b = m & 1, s = m % STAGES;
+        TRACE(2, m, 2);
         ok = mbar_wait(&bar_p_ready[b], (m >> 1) & 1);
         if (!ok) return;
+        TRACE(2, m, 3);
         tc_fence_after();
         if (!(PV_SKIP && s_skip[b])) {
           const uint32_t vaddr = smem_u32(sKV + s * 2 * Shape::kTileKV + Shape::kTileKV);
@@ -182,11 +193,14 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         }
         tc_commit(&bar_kv_empty[s]);
         tc_commit(&bar_o_done);
+        TRACE(2, m, 4);
       };
       for (int n = 0; n < cnt && ok; n++) {
         const int s = n % STAGES;
+        TRACE(2, n, 0);
         ok = mbar_wait(&bar_kv_full[s], (n / STAGES) & 1);
         if (!ok) break;
+        TRACE(2, n, 1);
         tc_fence_after();
         const uint32_t qaddr = smem_u32(sQ), kaddr = smem_u32(sKV + s * 2 * Shape::kTileKV);
 #pragma unroll
@@ -209,30 +223,42 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     const float qs = q_scale[row_id] * sm_scale_log2;
     const float thr = PV_SKIP ? pvthr[h] : 0.f;
     const float* ksc = k_scale + (size_t)bh * nk;
+    // A run-time 1 that the compiler cannot fold: multiplying by it turns the int->float bias add
+    // into an IMAD, which issues on the full-rate FMA pipe instead of the half-rate integer pipe.
+    const int one = (nq > 0) ? 1 : 0;
     float m = kMaskValue, d = 0.f;
-    // block index and dequantisation factor are fetched one iteration ahead of their use
-    int j_next = max(0, min(lrow[0], nk - 1));
-    float c_next = qs * ksc[j_next];
+    // Software-pipelined metadata: the LUT delta is loaded two iterations ahead and the K scale one
+    // iteration ahead, and neither value is touched before the iteration after its load, so the two
+    // dependent global loads never stall the in-order issue of this warp.
+    int j_cur = max(0, min(lrow[0], nk - 1));
+    float ks_cur = ksc[j_cur];
+    int j_nxt = max(0, min(j_cur + ((cnt > 1) ? lrow[1] : 0), nk - 1));
+    float ks_nxt = ksc[j_nxt];
+    int delta_nn = (cnt > 2) ? lrow[2] : 0;
     bool ok = true;
     for (int n = 0; n < cnt; n++) {
-      const int j = j_next;
-      const float c = c_next;
-      if (n + 1 < cnt) {
-        j_next = max(0, min(j + lrow[n + 1], nk - 1));
-        c_next = qs * ksc[j_next];
-      }
+      const int j = j_cur;
+      const float c = qs * ks_cur;
+      j_cur = j_nxt;
+      ks_cur = ks_nxt;
+      j_nxt = max(0, min(j_nxt + delta_nn, nk - 1));
+      ks_nxt = ksc[j_nxt];                                 // consumed in iteration n+2
+      delta_nn = (n + 3 < cnt) ? lrow[n + 3] : 0;          // consumed in iteration n+1
       const int b = n & 1;
       const uint32_t tS = tbase + b * 64 + tlane;
+      if (tid == 0) TRACE(0, n, 0);
       ok = mbar_wait(&bar_s_full[b], (n >> 1) & 1);
       if (!ok) break;
+      if (tid == 0) TRACE(0, n, 1);
       tc_fence_after();
       uint32_t sr[64];
       tmem_ld32(tS, sr);
       tmem_ld32(tS + 32, sr + 32);
       tmem_wait_ld();
+      if (tid == 0) TRACE(0, n, 2);
       const int key0 = j * 64;
       const bool masked_block = (key0 + 64 > N) || (CAUSAL && (key0 + 63 > qi * 128));
-      // per-key mask limit for this row: keys with index >= klim are masked
+      // per-key mask limit for this row: keys with local index >= klim are masked
       int klim = 64;
       if (masked_block) {
         klim = min(64, N - key0);
@@ -240,17 +266,20 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         klim = max(klim, 0);
       }
       float rmax;
-      {
-        int mx = INT_MIN;
-        if (!masked_block) {
+      if (!masked_block) {
+        int m0 = (int)sr[0], m1 = (int)sr[32];
 #pragma unroll
-          for (int k = 0; k < 64; k++) mx = max(mx, (int)sr[k]);
-          rmax = __int2float_rn(mx) * c;
-        } else {
-#pragma unroll
-          for (int k = 0; k < 64; k++) mx = (k < klim) ? max(mx, (int)sr[k]) : mx;
-          rmax = (klim > 0) ? __int2float_rn(mx) * c : kMaskValue;
+        for (int k = 1; k < 31; k += 2) {
+          m0 = __vimax3_s32(m0, (int)sr[k], (int)sr[k + 1]);
+          m1 = __vimax3_s32(m1, (int)sr[32 + k], (int)sr[32 + k + 1]);
         }
+        const int mx = __vimax3_s32(max(m0, m1), (int)sr[31], (int)sr[63]);
+        rmax = (__int_as_float(mx + (int)kMagicBits) - kMagic) * c;   // c > 0: max commutes with the scaling
+      } else {
+        int mx = INT_MIN;
+#pragma unroll
+        for (int k = 0; k < 64; k++) mx = (k < klim) ? max(mx, (int)sr[k]) : mx;
+        rmax = (klim > 0) ? __int2float_rn(mx) * c : kMaskValue;
       }
       const float m_new = fmaxf(m, rmax);
       bool skip = false;
@@ -265,11 +294,15 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         const float dcta = fmaxf(fmaxf(s_delta[b][0], s_delta[b][1]), fmaxf(s_delta[b][2], s_delta[b][3]));
         skip = (dcta + thr <= 0.f);
       }
+      if (tid == 0) TRACE(0, n, 3);
       if (n > 0) {
-        ok = mbar_wait(&bar_o_done, (n - 1) & 1);
-        if (!ok) break;
         const float alpha = ex2_approx(m - m_new);
-        if (__any_sync(0xffffffffu, m_new > m)) {   // rescale the running output
+        if (__any_sync(0xffffffffu, m_new > m)) {   // some row of this warp raised its maximum: rescale O
+          // PV(n-1) must have landed before O is touched. Blocks <= n-2 are known complete (the commit
+          // behind s_full(n) covers them), so a parity wait on phase n-1 cannot alias even though
+          // iterations without a rescale skip this wait.
+          ok = mbar_wait(&bar_o_done, (n - 1) & 1);
+          if (!ok) break;
           tc_fence_after();
 #pragma unroll
           for (int c0 = 0; c0 < D; c0 += 32) {
@@ -284,37 +317,67 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         }
         d *= alpha;
       }
+      if (tid == 0) TRACE(0, n, 4);
       m = m_new;
       if (skip) {
         if (tid == 0) s_skip[b] = 1;
         tc_fence_before();
-        mbar_arrive(&bar_p_ready[b]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_p_ready[b]);
         continue;
       }
-      const float off = kFp8Offset - m;
       uint32_t pr[16];
-      float sum = 0.f;
+      float sum;
+      if (!masked_block) {
+        // int32 -> fp32 by adding the bit pattern of 1.5 * 2^23 (exact for |S| < 2^22; here |S| <= 127^2 * 128);
+        // the 2^23 bias is taken out again inside the FMA constant. Packed f32x2 FMA / ADD halve the issue slots.
+        const float off = fmaf(-kMagic, c, kFp8Offset - m);
+        const float2 c2 = make_float2(c, c), o2 = make_float2(off, off);
+        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int k = 0; k < 64; k += 4) {
-        float p0 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 0]), c, off));
-        float p1 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 1]), c, off));
-        float p2 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 2]), c, off));
-        float p3 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 3]), c, off));
-        if (masked_block) {
+        for (int k = 0; k < 64; k += 4) {
+          float2 a = make_float2(__int_as_float((int)sr[k + 0] * one + (int)kMagicBits),
+                                 __int_as_float((int)sr[k + 1] * one + (int)kMagicBits));
+          float2 bb = make_float2(__int_as_float((int)sr[k + 2] * one + (int)kMagicBits),
+                                  __int_as_float((int)sr[k + 3] * one + (int)kMagicBits));
+          a = __ffma2_rn(a, c2, o2);
+          bb = __ffma2_rn(bb, c2, o2);
+          a.x = ex2_approx(a.x);
+          a.y = ex2_approx(a.y);
+          bb.x = ex2_approx(bb.x);
+          bb.y = ex2_approx(bb.y);
+          s0 = __fadd2_rn(s0, a);
+          s1 = __fadd2_rn(s1, bb);
+          pr[k >> 2] = cvt_e4m3x4(a.x, a.y, bb.x, bb.y);
+        }
+        s0 = __fadd2_rn(s0, s1);
+        sum = s0.x + s0.y;
+      } else {
+        const float off = kFp8Offset - m;
+        sum = 0.f;
+#pragma unroll
+        for (int k = 0; k < 64; k += 4) {
+          float p0 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 0]), c, off));
+          float p1 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 1]), c, off));
+          float p2 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 2]), c, off));
+          float p3 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 3]), c, off));
           p0 = (k + 0 < klim) ? p0 : 0.f;
           p1 = (k + 1 < klim) ? p1 : 0.f;
           p2 = (k + 2 < klim) ? p2 : 0.f;
           p3 = (k + 3 < klim) ? p3 : 0.f;
+          sum += (p0 + p1) + (p2 + p3);
+          pr[k >> 2] = cvt_e4m3x4(p0, p1, p2, p3);
         }
-        sum += (p0 + p1) + (p2 + p3);
-        pr[k >> 2] = cvt_e4m3x4(p0, p1, p2, p3);
       }
       d += sum;
+      if (tid == 0) TRACE(0, n, 5);
       tmem_st16(tS, pr);
       tmem_wait_st();
       if (PV_SKIP && tid == 0) s_skip[b] = 0;
       tc_fence_before();
-      mbar_arrive(&bar_p_ready[b]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_p_ready[b]);
+      if (tid == 0) TRACE(0, n, 6);
     }
     if (ok) ok = mbar_wait(&bar_o_done, (cnt - 1) & 1);
     if (ok) {
