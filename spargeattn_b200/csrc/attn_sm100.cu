@@ -28,12 +28,6 @@ constexpr float kMaskValue = -5000000.0f;  // csrc/qattn/attn_utils.cuh:348-352
 constexpr uint32_t kMagicBits = 0x4B400000u;   // bit pattern of 12582912.0f = 1.5 * 2^23
 constexpr float kMagic = 12582912.0f;
 
-#ifdef SPARGE_EXP_TRACE
-#define TRACE(who, n, ev) do { if (blockIdx.x == 4 && blockIdx.y == 0 && (n) >= 8 && (n) < 24) \
-  reinterpret_cast<long long*>(dev_status + 16)[((who) * 16 + ((n) - 8)) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define TRACE(who, n, ev) do {} while (0)
-#endif
 
 template <int D>
 struct AttnShape {
@@ -68,7 +62,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
             const __grid_constant__ CUtensorMap tmap_v, OutT* __restrict__ o, const int32_t* __restrict__ lut,
             const int32_t* __restrict__ valid, const float* __restrict__ pvthr, const float* __restrict__ q_scale,
             const float* __restrict__ k_scale, const float* __restrict__ v_scale, int32_t* dev_status, int N, int H,
-            int nq, int nk, float sm_scale_log2) {
+            int nq, int nk, float sm_scale_log2, int one) {
   using Shape = AttnShape<D>;
   constexpr int STAGES = Shape::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -178,10 +172,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       bool ok = mbar_wait(&bar_q, 0);
       auto issue_pv = [&](int m) {
         const int b = m & 1, s = m % STAGES;
-        TRACE(2, m, 2);
         ok = mbar_wait(&bar_p_ready[b], (m >> 1) & 1);
         if (!ok) return;
-        TRACE(2, m, 3);
         tc_fence_after();
         if (!(PV_SKIP && s_skip[b])) {
           const uint32_t vaddr = smem_u32(sKV + s * 2 * Shape::kTileKV + Shape::kTileKV);
@@ -193,14 +185,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         }
         tc_commit(&bar_kv_empty[s]);
         tc_commit(&bar_o_done);
-        TRACE(2, m, 4);
       };
       for (int n = 0; n < cnt && ok; n++) {
         const int s = n % STAGES;
-        TRACE(2, n, 0);
         ok = mbar_wait(&bar_kv_full[s], (n / STAGES) & 1);
         if (!ok) break;
-        TRACE(2, n, 1);
         tc_fence_after();
         const uint32_t qaddr = smem_u32(sQ), kaddr = smem_u32(sKV + s * 2 * Shape::kTileKV);
 #pragma unroll
@@ -223,9 +212,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     const float qs = q_scale[row_id] * sm_scale_log2;
     const float thr = PV_SKIP ? pvthr[h] : 0.f;
     const float* ksc = k_scale + (size_t)bh * nk;
-    // A run-time 1 that the compiler cannot fold: multiplying by it turns the int->float bias add
-    // into an IMAD, which issues on the full-rate FMA pipe instead of the half-rate integer pipe.
-    const int one = (nq > 0) ? 1 : 0;
+    // `one` is a kernel argument equal to 1 that the compiler cannot fold: multiplying by it turns the
+    // int->float bias add into an IMAD, which issues on the FMA pipe instead of the half-rate integer pipe.
     float m = kMaskValue, d = 0.f;
     // Software-pipelined metadata: the LUT delta is loaded two iterations ahead and the K scale one
     // iteration ahead, and neither value is touched before the iteration after its load, so the two
@@ -246,16 +234,13 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       delta_nn = (n + 3 < cnt) ? lrow[n + 3] : 0;          // consumed in iteration n+1
       const int b = n & 1;
       const uint32_t tS = tbase + b * 64 + tlane;
-      if (tid == 0) TRACE(0, n, 0);
       ok = mbar_wait(&bar_s_full[b], (n >> 1) & 1);
       if (!ok) break;
-      if (tid == 0) TRACE(0, n, 1);
       tc_fence_after();
       uint32_t sr[64];
       tmem_ld32(tS, sr);
       tmem_ld32(tS + 32, sr + 32);
       tmem_wait_ld();
-      if (tid == 0) TRACE(0, n, 2);
       const int key0 = j * 64;
       const bool masked_block = (key0 + 64 > N) || (CAUSAL && (key0 + 63 > qi * 128));
       // per-key mask limit for this row: keys with local index >= klim are masked
@@ -294,7 +279,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         const float dcta = fmaxf(fmaxf(s_delta[b][0], s_delta[b][1]), fmaxf(s_delta[b][2], s_delta[b][3]));
         skip = (dcta + thr <= 0.f);
       }
-      if (tid == 0) TRACE(0, n, 3);
       if (n > 0) {
         const float alpha = ex2_approx(m - m_new);
         if (__any_sync(0xffffffffu, m_new > m)) {   // some row of this warp raised its maximum: rescale O
@@ -309,15 +293,19 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
             uint32_t ov[32];
             tmem_ld32(tO + tlane + c0, ov);
             tmem_wait_ld();
+            const float2 al2 = make_float2(alpha, alpha);
 #pragma unroll
-            for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            for (int i = 0; i < 32; i += 2) {
+              const float2 r2 = __fmul2_rn(make_float2(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1])), al2);
+              ov[i] = __float_as_uint(r2.x);
+              ov[i + 1] = __float_as_uint(r2.y);
+            }
             tmem_st32(tO + tlane + c0, ov);
           }
           tmem_wait_st();
         }
         d *= alpha;
       }
-      if (tid == 0) TRACE(0, n, 4);
       m = m_new;
       if (skip) {
         if (tid == 0) s_skip[b] = 1;
@@ -370,14 +358,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         }
       }
       d += sum;
-      if (tid == 0) TRACE(0, n, 5);
       tmem_st16(tS, pr);
       tmem_wait_st();
       if (PV_SKIP && tid == 0) s_skip[b] = 0;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_p_ready[b]);
-      if (tid == 0) TRACE(0, n, 6);
     }
     if (ok) ok = mbar_wait(&bar_o_done, (cnt - 1) & 1);
     if (ok) {
@@ -453,7 +439,7 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   const int nq = (N + 127) / 128, nk = (N + 63) / 64;
   kern<<<dim3(nq, BH), 192, smem, st>>>(tq, tk, tv, (OutT*)o, lut, valid, pvthr, qs, ks, vs, status, N, H, nq, nk,
-                                        sm_scale_log2);
+                                        sm_scale_log2, 1);
   return launch_status();
 }
 

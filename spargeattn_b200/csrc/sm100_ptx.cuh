@@ -54,14 +54,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. Returns false when the phase did not complete in time.
+// Each try_wait may suspend the thread for up to kWaitSliceNs (it resumes as soon as the phase
+// completes), so a waiting role costs a handful of instructions per slice instead of a hot spin;
+// kWaitSlices slices bound the total wait to about one second.
+constexpr uint32_t kWaitSliceNs = 1000000u;   // 1 ms
+constexpr uint32_t kWaitSlices = 1000u;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t it = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (((++it) & 0x3ff) == 0 && (clock64() - t0) > SPARGE_WAIT_LIMIT_CYCLES) return false;
-  }
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P1, P2;\n\t"
+      ".reg .u32 cnt;\n\t"
+      "mov.u32 cnt, 0;\n\t"
+      "SPARGE_WAIT:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\n\t"
+      "@P1 bra SPARGE_DONE;\n\t"
+      "add.u32 cnt, cnt, 1;\n\t"
+      "setp.lt.u32 P2, cnt, %4;\n\t"
+      "@P2 bra SPARGE_WAIT;\n\t"
+      "SPARGE_DONE:\n\t"
+      "selp.u32 %0, 1, 0, P1;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitSliceNs), "r"(kWaitSlices)
+      : "memory");
+  return ok != 0;
 }
 
 // ---------------------------------------------------------------- TMA (tiled, no multicast)
@@ -77,6 +94,12 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, ui
       ::"r"(smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+
+// Makes this thread's earlier generic-proxy writes to shared memory visible to the async proxy
+// (TMA, tcgen05.mma operand fetch).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- TMEM
