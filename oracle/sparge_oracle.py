@@ -14,8 +14,9 @@ Where the reference leaves a summation order or a division instruction to a libr
 (Triton reductions, cuBLAS, torch softmax/sort), this file pins one choice, stated at each
 function, and the CUDA kernels implement the same choice so that they can be compared
 bit for bit:
-  * reductions over rows / channels accumulate in fp64 (order-free to ~1e-16) and are
-    rounded to fp32 once;
+  * the K mean and the softmax accumulate in fp64 (order-free to ~1e-16) and are rounded to
+    fp32 once; block pooling and row norms use short fp32 running sums in a fixed order,
+    combined in fp64 / by a fixed butterfly (see pool_sim_quant);
   * fp32 divisions are IEEE round-to-nearest;
   * the pooled score is an fp32 FMA chain over ascending channel index;
   * the row softmax is evaluated in fp64, rounded to fp32, then to the 16-bit dtype;
@@ -132,21 +133,44 @@ def pool_sim_quant(x: torch.Tensor, km: Optional[torch.Tensor], bs: int, simthre
     if not want_pool:
         return None, None, x_int8, scale
 
+    # Pinned reduction orders (the CUDA kernel uses the same ones, see csrc/pool_quant.cu):
+    #   rows:     fp32 running sum over each run of 8 consecutive rows, fp64 across the runs
+    #   channels: fp32 running sum of squares over each run of 8 consecutive channels, then an
+    #             fp32 butterfly (partner = index xor D/16, ..., xor 1) across the D/8 runs
+    def rows8(t):                                                     # [B,H,nb,bs,D] fp32 -> [B,H,nb,D] fp64
+        g = t.view(B, H, nb, bs // 8, 8, D)
+        acc = g[..., 0, :].clone()
+        for i in range(1, 8):
+            acc = acc + g[..., i, :]
+        return acc.double().sum(dim=-2)
+
     # utils.py:182,192 -- pool = sum over rows / BS_  (BS_ = rows actually present)
     bs_ = valid.sum(-1).to(torch.float32)                            # [nb]
-    pool = (x32.double().sum(dim=-2).float() / bs_.view(1, 1, nb, 1)).to(x.dtype)
+    pool = (rows8(x32).float() / bs_.view(1, 1, nb, 1)).to(x.dtype)
 
     # utils.py:193-199 -- x_hat = fp16(x / ||x||), sim = sum_ij <x_hat_i, x_hat_j> / BS_^2 > thr
-    # using  sum_ij <a_i, a_j> = || sum_i a_i ||^2 .
-    nrm = (x32.double() ** 2).sum(dim=-1, keepdim=True).float().sqrt()
-    xhat = (x32 / nrm).to(torch.float16)                             # 0/0 -> NaN on empty rows
-    ssum = xhat.double().sum(dim=-2)                                 # [B,H,nb,D]
+    # using  sum_ij <a_i, a_j> = || sum_i a_i ||^2 ; the division is one IEEE reciprocal per row
+    # followed by a multiplication per element.
+    sq = (x32 * x32).view(B, H, nb, bs, D // 8, 8)                    # products of 16-bit values are exact
+    part = sq[..., 0].clone()
+    for i in range(1, 8):
+        part = part + sq[..., i]
+    tpr = D // 8
+    o = tpr // 2
+    while o >= 1:
+        part = part + part[..., torch.arange(tpr) ^ o]
+        o //= 2
+    nrm = part[..., :1].sqrt()                                        # [B,H,nb,bs,1]
+    rinv = torch.ones_like(nrm) / nrm
+    xhat = (x32 * rinv).to(torch.float16)                             # 0 * inf -> NaN on empty rows
+    zero_row = (nrm.squeeze(-1) == 0).any(dim=-1)
+    xhat = torch.where(nrm == 0, torch.zeros((), dtype=torch.float16), xhat)
+    ssum = rows8(xhat.float())                                        # [B,H,nb,D] fp64
     total = (ssum * ssum).sum(dim=-1).float()
     simval = total / (bs_ * bs_).view(1, 1, nb)
-    sim = simval > simthreshd1.view(1, H, 1)                          # NaN compares False
+    sim = simval > simthreshd1.view(1, H, 1)
     full = (valid.sum(-1) == bs).view(1, 1, nb)
-    zero_row = (nrm.squeeze(-1) == 0).any(dim=-1)
-    sim = sim & full & ~zero_row                                     # explicit form of the NaN rule
+    sim = sim & full & ~zero_row                                     # explicit form of the reference's NaN rule
     return pool, sim, x_int8, scale
 
 

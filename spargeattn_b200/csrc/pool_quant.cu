@@ -4,29 +4,54 @@
 // qk_quantize (utils.py:89-159).
 //
 // Arithmetic contract (shared with the CPU oracle):
-//   * sums over rows / channels accumulate in fp64 and are rounded to fp32 once;
-//   * the self-similarity uses  sum_ij <a_i, a_j> = || sum_i a_i ||^2  with a_i = fp16(x_i / ||x_i||);
+//   * row sums (pool, sum of unit vectors): fp32 running sum over each run of 8 consecutive rows,
+//     fp64 across the runs, one rounding to fp32;
+//   * row norms: fp32 running sum of squares over each run of 8 consecutive channels, then an fp32
+//     butterfly (partner = index xor D/16 ... xor 1) across the D/8 runs; sqrt and 1/x are IEEE;
+//   * the self-similarity uses  sum_ij <a_i, a_j> = || sum_i a_i ||^2  with a_i = fp16(x_i * (1/||x_i||));
 //   * a block with fewer than `BS` rows, or with an all-zero row, is never self-similar
 //     (the reference gets there through a 0/0 NaN, utils.py:194-199);
-//   * scale = max|x| / 127 + 1e-7, q = trunc(x / scale + 0.5 * sign), IEEE fp32 division.
+//   * scale = max|x| / 127 + 1e-7, q = trunc(x / scale + 0.5 * sign) with the IEEE quotient.
+// The quotient is formed without a per-element division: with r = RN(1/scale), y0 = x*r,
+// e = fma(-scale, y0, x) (exact remainder), y = fma(e, r, y0) is the correctly rounded x/scale.
 #include "common.cuh"
 
 namespace sparge {
 
+template <typename T>
+__device__ __forceinline__ float unpack16(uint32_t w, int hi);
+template <>
+__device__ __forceinline__ float unpack16<__nv_bfloat16>(uint32_t w, int hi) {
+  return __uint_as_float(hi ? (w & 0xffff0000u) : (w << 16));
+}
+template <>
+__device__ __forceinline__ float unpack16<__half>(uint32_t w, int hi) {
+  return __half2float(__ushort_as_half((unsigned short)(hi ? (w >> 16) : (w & 0xffffu))));
+}
+template <typename T>
+__device__ __forceinline__ uint32_t bits16(float v);
+template <>
+__device__ __forceinline__ uint32_t bits16<__nv_bfloat16>(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
+template <>
+__device__ __forceinline__ uint32_t bits16<__half>(float v) { return __half_as_ushort(__float2half_rn(v)); }
+
+// Thread layout: TPR = D/8 threads per row (8 channels each), G = BS/8 row groups; thread (g, cg)
+// owns rows 8g..8g+7 of channel group cg. blockDim = G * TPR (64 .. 256).
 template <typename T, int D, int BS, bool HAS_KM, bool WANT_POOL>
-__global__ void __launch_bounds__(256) pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km,
-                                                         const float* __restrict__ simthr, T* __restrict__ pool,
-                                                         uint8_t* __restrict__ sim, int8_t* __restrict__ xq,
-                                                         float* __restrict__ scale_out, int N, int H, int nb) {
-  constexpr int TPR = D / 8;          // threads per row (8 or 16)
-  constexpr int RPP = 256 / TPR;      // rows per pass (32 or 16)
-  constexpr int PASSES = BS / RPP;
-  __shared__ double red[RPP][D];      // 16 KB
-  __shared__ float s_amax[8];
-  __shared__ double s_tot[8];
+__global__ void __launch_bounds__((BS / 8) * (D / 8))
+pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float* __restrict__ simthr,
+                  T* __restrict__ pool, uint8_t* __restrict__ sim, int8_t* __restrict__ xq,
+                  float* __restrict__ scale_out, int N, int H, int nb) {
+  constexpr int TPR = D / 8;
+  constexpr int G = BS / 8;
+  constexpr int NT = G * TPR;
+  constexpr int NW = NT / 32;
+  __shared__ float s_part[WANT_POOL ? 2 : 1][WANT_POOL ? G : 1][WANT_POOL ? D : 1];   // pooled / unit-vector partials
+  __shared__ float s_amax[NW];
+  __shared__ double s_tot[D / 32];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int cg = tid % TPR, r0 = tid / TPR;
+  const int cg = tid % TPR, g = tid / TPR;
   const int blk = blockIdx.x, bh = blockIdx.y;
   const int row_base = blk * BS;
   const int rows_here = min(BS, N - row_base);
@@ -34,51 +59,65 @@ __global__ void __launch_bounds__(256) pool_quant_kernel(const T* __restrict__ x
 
   float kmv[8];
   if (HAS_KM) {
-    Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(km + (size_t)bh * D + cg * 8);
+    const uint4 p = *reinterpret_cast<const uint4*>(km + (size_t)bh * D + cg * 8);
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
-    for (int i = 0; i < 8; i++) kmv[i] = Elem<T>::to_float(p.v[i]);
+    for (int i = 0; i < 8; i++) kmv[i] = unpack16<T>(w[i >> 1], i & 1);
   }
 
-  float xv[PASSES][8];
-  float amax = 0.f;
-  double pacc[8], hacc[8];
+  // ---- load the thread's 8 rows (all loads in flight before the first use)
+  uint4 raw[8];
 #pragma unroll
-  for (int i = 0; i < 8; i++) { pacc[i] = 0.0; hacc[i] = 0.0; }
+  for (int i = 0; i < 8; i++) {
+    const int row = g * 8 + i;
+    raw[i] = (row < rows_here) ? *reinterpret_cast<const uint4*>(xb + (size_t)row * D + cg * 8) : make_uint4(0, 0, 0, 0);
+  }
+
+  float amax = 0.f;
+  float pacc[8], hacc[8];
+#pragma unroll
+  for (int c = 0; c < 8; c++) { pacc[c] = 0.f; hacc[c] = 0.f; }
   int zero_row = 0;
 
 #pragma unroll
-  for (int p = 0; p < PASSES; p++) {
-    const int row = r0 + p * RPP;
-    const bool valid = row < rows_here;
-    if (valid) {
-      Pack8<T> pk = *reinterpret_cast<const Pack8<T>*>(xb + (size_t)row * D + cg * 8);
+  for (int i = 0; i < 8; i++) {
+    const bool valid = (g * 8 + i) < rows_here;
+    uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+    float v[8];
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        float v = Elem<T>::to_float(pk.v[i]);
-        if (HAS_KM) v = Elem<T>::to_float(Elem<T>::from_float(__fsub_rn(v, kmv[i])));
-        xv[p][i] = v;
-        amax = fmaxf(amax, fabsf(v));
+    for (int c = 0; c < 8; c++) v[c] = unpack16<T>(w[c >> 1], c & 1);
+    if (HAS_KM) {
+      if (valid) {
+#pragma unroll
+        for (int c = 0; c < 8; c += 2) {   // subtraction rounded to the 16-bit type; keep the rounded bits
+          const uint32_t lo = bits16<T>(__fsub_rn(v[c], kmv[c])), hi = bits16<T>(__fsub_rn(v[c + 1], kmv[c + 1]));
+          w[c >> 1] = lo | (hi << 16);
+        }
+        raw[i] = make_uint4(w[0], w[1], w[2], w[3]);
+#pragma unroll
+        for (int c = 0; c < 8; c++) v[c] = unpack16<T>(w[c >> 1], c & 1);
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; i++) xv[p][i] = 0.f;
     }
+    amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+                             fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7])))));
     if (WANT_POOL) {
-      double ss = 0.0;
+      float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        pacc[i] += (double)xv[p][i];
-        ss += (double)xv[p][i] * (double)xv[p][i];
+      for (int c = 0; c < 8; c++) {
+        pacc[c] = __fadd_rn(pacc[c], v[c]);
+        ss = __fmaf_rn(v[c], v[c], ss);
       }
 #pragma unroll
-      for (int o = TPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float nrm = __fsqrt_rn((float)ss);
+      for (int o = TPR / 2; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+      const float nrm = __fsqrt_rn(ss);
       if (valid) {
         if (nrm == 0.f) {
           zero_row = 1;
         } else {
+          const float rinv = __fdiv_rn(1.0f, nrm);
 #pragma unroll
-          for (int i = 0; i < 8; i++) hacc[i] += (double)__half2float(__float2half_rn(__fdiv_rn(xv[p][i], nrm)));
+          for (int c = 0; c < 8; c++)
+            hacc[c] = __fadd_rn(hacc[c], __half2float(__float2half_rn(__fmul_rn(v[c], rinv))));
         }
       }
     }
@@ -87,56 +126,59 @@ __global__ void __launch_bounds__(256) pool_quant_kernel(const T* __restrict__ x
   // ---- block amax -> scale
   amax = warp_max(amax);
   if (lane == 0) s_amax[warp] = amax;
-  __syncthreads();
+  if (WANT_POOL) {
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      s_part[0][g][cg * 8 + c] = pacc[c];
+      s_part[WANT_POOL ? 1 : 0][g][cg * 8 + c] = hacc[c];
+    }
+  }
+  const int any_zero = __syncthreads_or(zero_row);
   amax = s_amax[0];
 #pragma unroll
-  for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_amax[w]);
+  for (int w = 1; w < NW; w++) amax = fmaxf(amax, s_amax[w]);
   const float scale = __fadd_rn(__fdiv_rn(amax, 127.0f), 1e-7f);
+  const float rs = __fdiv_rn(1.0f, scale);
   if (tid == 0) scale_out[(size_t)bh * nb + blk] = scale;
 
   // ---- quantise from registers
   int8_t* qb = xq + ((size_t)bh * N + row_base) * D;
 #pragma unroll
-  for (int p = 0; p < PASSES; p++) {
-    const int row = r0 + p * RPP;
+  for (int i = 0; i < 8; i++) {
+    const int row = g * 8 + i;
     if (row < rows_here) {
-      uint32_t w[2] = {0u, 0u};
+      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+      uint32_t out[2] = {0u, 0u};
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        float y = __fdiv_rn(xv[p][i], scale);
+      for (int c = 0; c < 8; c++) {
+        const float xv = unpack16<T>(w[c >> 1], c & 1);
+        const float y0 = __fmul_rn(xv, rs);
+        const float e = __fmaf_rn(-scale, y0, xv);
+        float y = __fmaf_rn(e, rs, y0);                      // == RN(xv / scale)
         y = __fadd_rn(y, y >= 0.f ? 0.5f : -0.5f);
-        const int q = (int)y;   // truncation toward zero
-        w[i >> 2] |= (uint32_t)(q & 0xff) << ((i & 3) * 8);
+        const int q = (int)y;                                // truncation toward zero
+        out[c >> 2] |= (uint32_t)(q & 0xff) << ((c & 3) * 8);
       }
-      *reinterpret_cast<uint2*>(qb + (size_t)row * D + cg * 8) = make_uint2(w[0], w[1]);
+      *reinterpret_cast<uint2*>(qb + (size_t)row * D + cg * 8) = make_uint2(out[0], out[1]);
     }
   }
 
   if (WANT_POOL) {
-    // ---- pooled mean
-#pragma unroll
-    for (int i = 0; i < 8; i++) red[r0][cg * 8 + i] = pacc[i];
-    const int any_zero = __syncthreads_or(zero_row);
-    if (tid < D) {
-      double s = 0.0;
-#pragma unroll 4
-      for (int r = 0; r < RPP; r++) s += red[r][tid];
-      pool[((size_t)bh * nb + blk) * D + tid] = Elem<T>::from_float(__fdiv_rn((float)s, (float)rows_here));
-    }
-    __syncthreads();
-    // ---- || sum_i a_i ||^2
-#pragma unroll
-    for (int i = 0; i < 8; i++) red[r0][cg * 8 + i] = hacc[i];
-    __syncthreads();
     double sq = 0.0;
     if (tid < D) {
-      double s = 0.0;
-#pragma unroll 4
-      for (int r = 0; r < RPP; r++) s += red[r][tid];
-      sq = s * s;
+      double ps = 0.0, hs = 0.0;
+#pragma unroll
+      for (int r = 0; r < G; r++) {
+        ps += (double)s_part[0][r][tid];
+        hs += (double)s_part[WANT_POOL ? 1 : 0][r][tid];
+      }
+      pool[((size_t)bh * nb + blk) * D + tid] = Elem<T>::from_float(__fdiv_rn((float)ps, (float)rows_here));
+      sq = hs * hs;
     }
-    sq = warp_sum(sq);
-    if (lane == 0) s_tot[warp] = sq;
+    if (warp < D / 32) {
+      sq = warp_sum(sq);
+      if (lane == 0) s_tot[warp] = sq;
+    }
     __syncthreads();
     if (tid == 0) {
       double tot = 0.0;
@@ -157,7 +199,7 @@ static int launch_pq(const void* x, const void* km, const float* thr, void* pool
   dim3 grid(nb, BH);
   const bool has_km = km != nullptr, want = thr != nullptr;
 #define SPARGE_PQ(KM, WP)                                                                                         \
-  pool_quant_kernel<T, D, BS, KM, WP><<<grid, 256, 0, st>>>((const T*)x, (const T*)km, thr, (T*)pool, sim, xq, sc, \
+  pool_quant_kernel<T, D, BS, KM, WP><<<grid, (BS / 8) * (D / 8), 0, st>>>((const T*)x, (const T*)km, thr, (T*)pool, sim, xq, sc, \
                                                             N, H, nb)
   if (has_km && want) SPARGE_PQ(true, true);
   else if (has_km) SPARGE_PQ(true, false);
