@@ -57,11 +57,14 @@ def dense_equiv_ops(B, H, N, D, causal):
     return ops / 2 if causal else ops
 
 
-def config_dict(idx, w, topk, n_gpus):
+def config_dict(idx, w, topk, n_gpus, ulysses=False):
     B, H, N, D = workload_shape(w)
+    sharding = (f"Ulysses sequence parallel over {n_gpus} GPUs: N/{n_gpus} tokens per rank, NCCL all-to-all to "
+                f"{H // n_gpus} heads per rank and back (strong scaling)") if ulysses else \
+        f"{n_gpus} x full head set (weak scaling, no collective)"
     return {"workload": f"cfg{idx}:{w['name']} B={B} H={H} N={N} D={D} bf16 {'causal' if w['causal'] else 'non-causal'} "
                         f"topk={topk} pvthreshd=50 (API default)",
-            "per_gpu_heads": H, "sharding": f"{n_gpus} x full head set (weak scaling, no collective)",
+            "per_gpu_heads": H // n_gpus if ulysses else H, "sharding": sharding,
             "l2_policy": "inputs larger than L2 (q,k,v = %.0f MB per rank)" % (3 * B * H * N * D * 2 / 1e6)}
 
 
@@ -185,13 +188,23 @@ def main():
 
     B, H, N, D = workload_shape(w)
     causal = w["causal"]
-    gen_seed_shift = rank  # every rank works on its own data
+    # workload 4 on several GPUs: Ulysses sequence parallelism (strong scaling, two all-to-alls per call);
+    # every other case: each rank runs the full head set on its own data (weak scaling, no collective)
+    ulysses = world > 1 and w.get("ulysses", False)
+    gen_seed_shift = 0 if ulysses else rank
     if w["kind"] == "llm":
         q, k, v = synthetic.llm_prefill_qkv(B, H, N, D, idx + 100 * gen_seed_shift, dev)
     else:
         q, k, v = synthetic.video_qkv(B, H, w["grid"], D, idx + 100 * gen_seed_shift, dev, w.get("text", 0),
                                       w.get("text_first", True))
-    api = lambda a, b, c: S.spas_sage2_attn_meansim_topk_cuda(a, b, c, topk=topk, is_causal=causal)
+    if ulysses:
+        from spargeattn_b200.sharding import ulysses_attention
+        assert N % world == 0 and H % world == 0
+        n_loc = N // world
+        q, k, v = (t[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous() for t in (q, k, v))
+        api = lambda a, b, c: ulysses_attention(a, b, c, topk=topk, is_causal=causal)
+    else:
+        api = lambda a, b, c: S.spas_sage2_attn_meansim_topk_cuda(a, b, c, topk=topk, is_causal=causal)
 
     def barrier():
         torch.cuda.synchronize()
@@ -220,14 +233,14 @@ def main():
     with ClockSampler(local) as clk:
         ms_step = timed(lambda: api(q, k, v), args.steps)
     ops.check_device_status(dev)
-    total_ops = dense_equiv_ops(B, H, N, D, causal) * world
+    total_ops = dense_equiv_ops(B, H, N, D, causal) * (1 if ulysses else world)
     value = total_ops / (ms_step * 1e-3) / 1e12
 
     if args.quick:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                               "warmup": args.warmup, "ms_per_step": ms_step, "quick": True,
-                              "config": config_dict(idx, w, topk, world)}))
+                              "config": config_dict(idx, w, topk, world, ulysses)}))
         if dist is not None:
             dist.destroy_process_group()
         return
@@ -252,7 +265,7 @@ def main():
 
     # ---- per-kernel timings on this rank (CUDA events on the launching stream)
     kernels, roofline = {}, None
-    if rank == 0:
+    if rank == 0 and not ulysses:
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -324,9 +337,10 @@ def main():
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "strong" if ulysses else "weak",
                 "vs_baseline": None, "dtype": "int8-qk/fp8-pv", "data": "synthetic",
-                "config": config_dict(idx, w, topk, world), "clocks": clk.summary(),
+                "config": config_dict(idx, w, topk, world, ulysses), "clocks": clk.summary(),
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": in_bytes,
                         "d2h_bytes_per_step": out_bytes},
                 "gpu_launches": GPU_LAUNCHES_PER_STEP * args.steps, "roofline": roofline, "kernels": kernels,

@@ -99,7 +99,7 @@ WORKLOADS = {
     2: dict(name="wan2.1_1.3b_480p", kind="video", B=1, H=12, D=128, grid=(21, 39, 40), text=0, topk=0.5, causal=False),
     3: dict(name="llama3_8b_prefill_32k", kind="llm", B=1, H=32, D=128, N=32768, topk=0.5, causal=True),
     4: dict(name="hunyuanvideo_720p", kind="video", B=1, H=24, D=128, grid=(33, 45, 80), text=256, text_first=False,
-            topk=0.4, causal=False),
+            topk=0.4, causal=False, ulysses=True),
 }
 
 
