@@ -206,7 +206,8 @@ def select_blocks(p: torch.Tensor, sim_q: torch.Tensor, sim_k: torch.Tensor, top
     order = torch.sort(p.float(), dim=-1, descending=True, stable=True)
     if cdfthreshd is not None:
         # utils.py:398-403: cumulative sum of the sorted probabilities, kept in the 16-bit dtype.
-        cdf = torch.cumsum(order.values, dim=-1).to(p.dtype).float()
+        # Pinned: the running sum is exact (fp64), rounded to fp32 and then to the 16-bit dtype per element.
+        cdf = torch.cumsum(order.values.double(), dim=-1).float().to(p.dtype).float()
         thr = cdfthreshd.view(1, H, 1, 1).expand(B, H, nq, 1).contiguous()
         n_sel = torch.searchsorted(cdf, thr, right=True).squeeze(-1)
     else:

@@ -9,8 +9,8 @@
 //   p      = T( float( exp(double(score) - max) / sum ) )           (fp64 softmax)
 //   top-k  = first n_sel of a stable descending order of p (ties -> lower block index),
 //            n_sel = clamp(int(topk[h] * nk), 1, nk)
-//   cdf    = n_sel = #{ r : T(prefix_r) <= cdfthreshd[h] } over that order, prefix in fp32,
-//            clamped to [1, nk]
+//   cdf    = n_sel = #{ r : T(float(prefix_r)) <= cdfthreshd[h] } over that order, prefix_r the exact
+//            (fp64) running sum of the sorted probabilities, clamped to [1, nk]
 #include <cfloat>
 
 #include "common.cuh"
@@ -64,157 +64,201 @@ __device__ __forceinline__ float key_value<__nv_bfloat16>(uint32_t k) {
   return __bfloat162float(__ushort_as_bfloat16((unsigned short)k));
 }
 
-// dynamic smem: double e[nk] | uint32 key[nk] | int idx[nk] | float qrow[D]
+// ---- warp-per-row predictor --------------------------------------------------------------------
+// One warp owns one (b, h, q-block) row; a CTA holds up to 4 consecutive rows of one head, so the
+// pooled K rows it streams are shared through L1. Everything is warp-synchronous (shuffles and
+// ballots), there is no block-wide barrier.
+// dynamic smem: [32][D*2+16] byte staging tile of pooled K rows (shared by the CTA's rows), then per
+// row: double e[nk] | uint32 key[nk] | int idx[nk] (also the fp32 scores) | float q[D]
+constexpr int kSelRowsPerCta = 4;
+
+__device__ __forceinline__ int warp_sum_int(int x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
 template <typename T, int D>
-__global__ void __launch_bounds__(kSelThreads) select_kernel(const T* __restrict__ pq, const T* __restrict__ pk,
-                                                             const uint8_t* __restrict__ sim_q,
-                                                             const uint8_t* __restrict__ sim_k,
-                                                             const float* __restrict__ topk,
-                                                             const float* __restrict__ cdfthr, uint8_t* __restrict__ mask,
-                                                             int32_t* __restrict__ lut, int32_t* __restrict__ valid, int H,
-                                                             int nq, int nk, int is_causal, int sink) {
+__global__ void __launch_bounds__(kSelRowsPerCta * 32)
+select_kernel(const T* __restrict__ pq, const T* __restrict__ pk, const uint8_t* __restrict__ sim_q,
+              const uint8_t* __restrict__ sim_k, const float* __restrict__ topk, const float* __restrict__ cdfthr,
+              uint8_t* __restrict__ mask, int32_t* __restrict__ lut, int32_t* __restrict__ valid, int H, int nq, int nk,
+              int is_causal, int sink, int rows_per_cta) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  double* s_e = reinterpret_cast<double*>(smem_raw);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int qi = blockIdx.x * rows_per_cta + warp, bh = blockIdx.y, h = bh % H;
+  const bool active = warp < rows_per_cta && qi < nq;       // inactive warps still help to stage K tiles
+  constexpr int kTileRowBytes = D * (int)sizeof(T) + 16;   // 16-byte pad: conflict-free 128-bit reads, one row per lane
+  unsigned char* s_tile = smem_raw;
+  const size_t row_bytes = (size_t)nk * 16 + D * sizeof(float);
+  unsigned char* base = smem_raw + 32 * kTileRowBytes + (size_t)(active ? warp : 0) * row_bytes;
+  double* s_e = reinterpret_cast<double*>(base);
   uint32_t* s_key = reinterpret_cast<uint32_t*>(s_e + nk);
   int* s_idx = reinterpret_cast<int*>(s_key + nk);
+  float* s_s = reinterpret_cast<float*>(s_idx);            // scores share storage with the index list
   float* s_q = reinterpret_cast<float*>(s_idx + nk);
-  __shared__ int s_warp[kSelThreads / 32];
-  __shared__ float s_fred[kSelThreads / 32];
-  __shared__ double s_dred[kSelThreads / 32];
-  __shared__ int s_hist[256];
-  __shared__ int s_sel[3];   // threshold byte, count above, remaining
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int qi = blockIdx.x, bh = blockIdx.y, h = bh % H;
   const int k_limit = is_causal ? min(nk, (qi + 1) * (kBlockQ / kBlockK)) : nk;   // causal: k < (q+1)*2
 
-  if (tid < D) s_q[tid] = Elem<T>::to_float(pq[((size_t)bh * nq + qi) * D + tid]);
-  __syncthreads();
+  if (active)
+    for (int dd = lane; dd < D; dd += 32) s_q[dd] = Elem<T>::to_float(pq[((size_t)bh * nq + qi) * D + dd]);
+  __syncwarp();
 
-  // ---- scores (kept as fp32 copies of the 16-bit values in the low half of s_e's storage)
-  float* s_s = reinterpret_cast<float*>(s_idx);   // reuse idx storage for the scores
+  // ---- scores: the CTA streams pooled K through shared memory in tiles of 32 rows (coalesced
+  // 128-bit loads); lane l of every active warp then runs the fp32 FMA chain for key block j0 + l.
   const float scale = (D == 64) ? 0.125f : 0.08838834764831845f;   // float(D ** -0.5)
   const T* pkb = pk + (size_t)bh * nk * D;
   const uint8_t* simk = sim_k + (size_t)bh * nk;
-  float lmax = -INFINITY;
-  for (int j = tid; j < nk; j += kSelThreads) {
-    float s = -INFINITY;
-    if (j < k_limit && simk[j]) {
-      float acc = 0.f;
-      const Pack8<T>* row = reinterpret_cast<const Pack8<T>*>(pkb + (size_t)j * D);
-#pragma unroll 4
-      for (int c = 0; c < D / 8; c++) {
-        Pack8<T> p = row[c];
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc = __fmaf_rn(s_q[c * 8 + i], Elem<T>::to_float(p.v[i]), acc);
-      }
-      s = Elem<T>::to_float(Elem<T>::from_float(acc));
-      s = Elem<T>::to_float(Elem<T>::from_float(__fmul_rn(s, scale)));
+  constexpr int kChunksPerRow = D * (int)sizeof(T) / 16;
+  float m = -INFINITY;
+  for (int j0 = 0; j0 < nk; j0 += 32) {
+    __syncthreads();                                       // previous tile fully consumed
+    for (int i = threadIdx.x; i < 32 * kChunksPerRow; i += blockDim.x) {
+      const int r = i / kChunksPerRow, c = i % kChunksPerRow;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (j0 + r < nk) val = *reinterpret_cast<const uint4*>(pkb + (size_t)(j0 + r) * D + c * 8);
+      *reinterpret_cast<uint4*>(s_tile + r * kTileRowBytes + c * 16) = val;
     }
-    s_s[j] = s;
-    lmax = fmaxf(lmax, s);
-  }
-  lmax = warp_max(lmax);
-  if (lane == 0) s_fred[warp] = lmax;
-  __syncthreads();
-  float m = s_fred[0];
+    __syncthreads();
+    const int j = j0 + lane;
+    if (active && j < nk) {
+      float sc = -INFINITY;
+      if (j < k_limit && simk[j]) {
+        float acc = 0.f;
+        const unsigned char* row = s_tile + lane * kTileRowBytes;
+#pragma unroll 4
+        for (int c = 0; c < kChunksPerRow; c++) {
+          const Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(row + c * 16);
 #pragma unroll
-  for (int w = 1; w < kSelThreads / 32; w++) m = fmaxf(m, s_fred[w]);
-
-  // ---- fp64 softmax
-  double lsum = 0.0;
-  for (int j = tid; j < nk; j += kSelThreads) {
-    const float s = s_s[j];
-    const double e = (s == -INFINITY) ? 0.0 : exp((double)s - (double)m);
-    s_e[j] = e;
-    lsum += e;
+          for (int i = 0; i < 8; i++) acc = __fmaf_rn(s_q[c * 8 + i], Elem<T>::to_float(p.v[i]), acc);
+        }
+        sc = Elem<T>::to_float(Elem<T>::from_float(acc));
+        sc = Elem<T>::to_float(Elem<T>::from_float(__fmul_rn(sc, scale)));
+      }
+      s_s[j] = sc;
+      m = fmaxf(m, sc);
+    }
   }
-  lsum = warp_sum(lsum);
-  if (lane == 0) s_dred[warp] = lsum;
-  __syncthreads();
+  if (!active) return;                                     // no block-wide barrier below this line
+  m = warp_max(m);
+
+  // ---- fp64 softmax -> 16-bit keys (p >= 0, so the bit pattern orders like the value)
   double Z = 0.0;
-#pragma unroll
-  for (int w = 0; w < kSelThreads / 32; w++) Z += s_dred[w];
-  const bool empty_row = (m == -INFINITY);
-  for (int j = tid; j < nk; j += kSelThreads) {
-    uint32_t key = 0;
-    if (!empty_row) key = key_bits<T>(Elem<T>::from_float((float)(s_e[j] / Z)));
-    s_key[j] = key;
+  for (int j = lane; j < nk; j += 32) {
+    const float sc = s_s[j];
+    const double e = (sc == -INFINITY) ? 0.0 : exp((double)sc - (double)m);
+    s_e[j] = e;
+    Z += e;
   }
-  __syncthreads();
+  Z = warp_sum(Z);
+  const bool empty_row = (m == -INFINITY);
+  for (int j = lane; j < nk; j += 32)
+    s_key[j] = empty_row ? 0u : key_bits<T>(Elem<T>::from_float((float)(s_e[j] / Z)));
+  __syncwarp();
 
-  // ---- how many to select (top-k mode: same count for every row of a head)
-  int n_sel = (int)__fmul_rn(topk[h], (float)nk);
+  // ---- how many blocks to select
+  int n_sel;
+  if (cdfthr == nullptr) {
+    n_sel = (int)__fmul_rn(topk[h], (float)nk);            // top-k mode: same count for every row of a head
+  } else {
+    // cdf mode: n_sel = #{ r : T(prefix_r) <= thr } over the descending order, prefix exact (fp64).
+    // Step 1: smallest key kappa such that the whole set {key >= kappa} stays within the threshold
+    // (16-step bisection; the set sum is monotone in kappa).
+    const float thr = cdfthr[h];
+    uint32_t lo = 0x10000u;                                // invariant: {key >= lo} fits (empty set at 0x10000)
+    {
+      uint32_t cand_hi = 0x10000u, cand_lo = 0u;           // search kappa in [0, 0x10000]
+      while (cand_lo < cand_hi) {
+        const uint32_t mid = (cand_lo + cand_hi) >> 1;
+        double sum = 0.0;
+        for (int j = lane; j < nk; j += 32) {
+          const uint32_t key = s_key[j];
+          if (key >= mid) sum += (double)key_value<T>(key);
+        }
+        sum = warp_sum(sum);
+        const bool fits = Elem<T>::to_float(Elem<T>::from_float((float)sum)) <= thr;
+        if (fits) cand_hi = mid; else cand_lo = mid + 1;
+      }
+      lo = cand_lo;
+    }
+    int cnt_full = 0;
+    double sum_full = 0.0;
+    uint32_t next_key = 0;                                 // largest key below lo
+    bool has_next = false;
+    for (int j = lane; j < nk; j += 32) {
+      const uint32_t key = s_key[j];
+      if (key >= lo) { cnt_full++; sum_full += (double)key_value<T>(key); }
+      else { next_key = max(next_key, key); has_next = true; }
+    }
+    cnt_full = warp_sum_int(cnt_full);
+    sum_full = warp_sum(sum_full);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) next_key = max(next_key, __shfl_xor_sync(0xffffffffu, next_key, o));
+    has_next = __any_sync(0xffffffffu, has_next);
+    n_sel = cnt_full;
+    if (has_next) {
+      // Step 2: part of the next run of equal keys may still fit: largest t with T(sum_full + t*v) <= thr.
+      int run = 0;
+      for (int j = lane; j < nk; j += 32) run += (s_key[j] == next_key);
+      run = warp_sum_int(run);
+      const double v = (double)key_value<T>(next_key);
+      int t_lo = 0, t_hi = run;                            // answer in [0, run]; t = run cannot fit by construction
+      while (t_lo < t_hi) {
+        const int t = (t_lo + t_hi + 1) >> 1;
+        const bool fits = Elem<T>::to_float(Elem<T>::from_float((float)(sum_full + (double)t * v))) <= thr;
+        if (fits) t_lo = t; else t_hi = t - 1;
+      }
+      n_sel += t_lo;
+    }
+  }
   n_sel = max(1, min(n_sel, nk));
 
-  // ---- 16-bit radix select of the n_sel-th largest key (two 8-bit digits)
-  int thr_key = 0, remaining = 0;
-  {
-    for (int i = tid; i < 256; i += kSelThreads) s_hist[i] = 0;
-    __syncthreads();
-    for (int j = tid; j < nk; j += kSelThreads) atomicAdd(&s_hist[s_key[j] >> 8], 1);
-    __syncthreads();
-    if (tid == 0) {
-      int acc = 0, b = 255;
-      for (; b > 0; b--) {
-        if (acc + s_hist[b] >= n_sel) break;
-        acc += s_hist[b];
-      }
-      s_sel[0] = b;
-      s_sel[1] = acc;
-    }
-    __syncthreads();
-    const int hb = s_sel[0];
-    const int above_hi = s_sel[1];
-    __syncthreads();
-    for (int i = tid; i < 256; i += kSelThreads) s_hist[i] = 0;
-    __syncthreads();
-    for (int j = tid; j < nk; j += kSelThreads) {
-      const uint32_t key = s_key[j];
-      if ((int)(key >> 8) == hb) atomicAdd(&s_hist[key & 0xff], 1);
-    }
-    __syncthreads();
-    if (tid == 0) {
-      int acc = above_hi, b = 255;
-      for (; b > 0; b--) {
-        if (acc + s_hist[b] >= n_sel) break;
-        acc += s_hist[b];
-      }
-      s_sel[0] = (hb << 8) | b;
-      s_sel[1] = acc;
-      s_sel[2] = n_sel - acc;
-    }
-    __syncthreads();
-    thr_key = s_sel[0];
-    remaining = s_sel[2];
+  // ---- n_sel-th largest key by bisection over the 16 key bits
+  uint32_t thr_key = 0;
+#pragma unroll 1
+  for (int bit = 15; bit >= 0; bit--) {
+    const uint32_t cand = thr_key | (1u << bit);
+    int c = 0;
+    for (int j = lane; j < nk; j += 32) c += (s_key[j] >= cand);
+    c = warp_sum_int(c);
+    if (c >= n_sel) thr_key = cand;
   }
+  int above = 0;
+  for (int j = lane; j < nk; j += 32) above += (s_key[j] > thr_key);
+  above = warp_sum_int(above);
+  const int remaining = n_sel - above;
 
-  // ---- final map, in index order (ties -> lower index), and compaction into idx[]
+  // ---- final map in index order (ties -> lower index) and compaction into idx[]
   const bool row_forced = sim_q[(size_t)bh * nq + qi] == 0;
   uint8_t* mrow = mask ? mask + ((size_t)bh * nq + qi) * nk : nullptr;
   int eq_seen = 0, live_seen = 0;
-  for (int j0 = 0; j0 < nk; j0 += kSelThreads) {
-    const int j = j0 + tid;
+  __syncwarp();                                            // scores are dead from here on: idx[] may overwrite them
+  for (int j0 = 0; j0 < nk; j0 += 32) {
+    const int j = j0 + lane;
     const bool in = j < nk;
     const uint32_t key = in ? s_key[j] : 0u;
-    const bool is_eq = in && (int)key == thr_key;
-    int eq_total;
-    const int eq_rank = eq_seen + block_exclusive_count(is_eq, s_warp, eq_total);
-    eq_seen += eq_total;
+    const bool is_eq = in && key == thr_key;
+    const unsigned eq_b = __ballot_sync(0xffffffffu, is_eq);
+    const int eq_rank = eq_seen + __popc(eq_b & ((1u << lane) - 1u));
+    eq_seen += __popc(eq_b);
     bool live = false;
     if (in) {
-      live = ((int)key > thr_key) || (is_eq && eq_rank < remaining) || row_forced || (simk[j] == 0);
+      live = (key > thr_key) || (is_eq && eq_rank < remaining) || row_forced || (simk[j] == 0);
       if (is_causal) live = live && (j < k_limit);
       if (sink && j == 0) live = true;
       if (mrow) mrow[j] = live ? 1 : 0;
     }
-    int live_total;
-    const int pos = live_seen + block_exclusive_count(live, s_warp, live_total);
-    live_seen += live_total;
-    if (live) s_idx[pos] = j;
+    const unsigned lv_b = __ballot_sync(0xffffffffu, live);
+    if (live) s_idx[live_seen + __popc(lv_b & ((1u << lane) - 1u))] = j;
+    live_seen += __popc(lv_b);
   }
-  __syncthreads();
-  write_lut_row(s_idx, live_seen, nk, lut + ((size_t)bh * nq + qi) * nk, valid + (size_t)bh * nq + qi);
+  __syncwarp();
+  int32_t* lrow = lut + ((size_t)bh * nq + qi) * nk;
+  for (int r = lane; r < nk; r += 32) {
+    int vv = 0;
+    if (r < live_seen) vv = s_idx[r] - (r > 0 ? s_idx[r - 1] : 0);
+    lrow[r] = vv;
+  }
+  if (lane == 0) valid[(size_t)bh * nq + qi] = live_seen;
 }
 
 // One CTA per mask row: compaction of a user block mask into the LUT.
@@ -253,15 +297,19 @@ template <typename T, int D>
 static int launch_select(const void* pq, const void* pk, const uint8_t* sim_q, const uint8_t* sim_k, const float* topk,
                          const float* cdf, uint8_t* mask, int32_t* lut, int32_t* valid, int BH, int H, int nq, int nk,
                          int causal, int sink, cudaStream_t st) {
-  const size_t smem = (size_t)nk * (sizeof(double) + sizeof(uint32_t) + sizeof(int)) + D * sizeof(float);
-  if (smem > 200 * 1024) return SPARGE_ERR_TOO_LARGE;
+  const size_t row_bytes = (size_t)nk * 16 + D * sizeof(float);
+  const size_t tile_bytes = 32 * (D * sizeof(T) + 16);
+  const size_t budget = 200 * 1024 - tile_bytes;
+  if (row_bytes > budget) return SPARGE_ERR_TOO_LARGE;
+  const int rows = (int)min((size_t)kSelRowsPerCta, budget / row_bytes);
+  const size_t smem = tile_bytes + rows * row_bytes;
   auto kern = select_kernel<T, D>;
   if (smem > 48 * 1024) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return SPARGE_ERR_CUDA;
   }
-  kern<<<dim3(nq, BH), kSelThreads, smem, st>>>((const T*)pq, (const T*)pk, sim_q, sim_k, topk, cdf, mask, lut, valid, H,
-                                                nq, nk, causal, sink);
+  kern<<<dim3((nq + rows - 1) / rows, BH), kSelRowsPerCta * 32, smem, st>>>(
+      (const T*)pq, (const T*)pk, sim_q, sim_k, topk, cdf, mask, lut, valid, H, nq, nk, causal, sink, rows);
   return launch_status();
 }
 
@@ -274,7 +322,6 @@ extern "C" int sparge_select(const void* pq, const void* pk, const uint8_t* sim_
   using namespace sparge;
   if (!pq || !pk || !sim_q || !sim_k || !lut || !valid) return SPARGE_ERR_NULL;
   if ((topk == nullptr) == (cdfthreshd == nullptr)) return SPARGE_ERR_INVALID_ARG;
-  if (cdfthreshd != nullptr) return SPARGE_ERR_UNSUPPORTED;   // cdf selection: not built yet
   if (B <= 0 || H <= 0 || nq <= 0 || nk <= 0 || (D != 64 && D != 128) || (dtype != SPARGE_F16 && dtype != SPARGE_BF16))
     return SPARGE_ERR_INVALID_ARG;
   if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;

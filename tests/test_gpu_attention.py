@@ -79,6 +79,22 @@ def test_block_sparse_api_matches_oracle(D):
     _check(o, o_ref)
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_cdf_api_matches_oracle(causal):
+    """spas_sage2_attn_meansim_cuda: cdf-threshold selection (what the reference's tuner calls)."""
+    import spargeattn_b200 as S
+    B, H, N, D = 1, 3, 1300, 128
+    q, k, v = _inputs(B, H, N, D, torch.bfloat16, 17)
+    cdf = torch.tensor([0.9, 0.95, 0.98])
+    (o_ref, sp_ref), _ = O.spas_sage2_attn_meansim_topk(q, k, v, is_causal=causal, simthreshd1=0.6, cdfthreshd=cdf,
+                                                        topk=None, return_sparsity=True, return_parts=True)
+    o, sp = S.spas_sage2_attn_meansim_cuda(q.cuda(), k.cuda(), v.cuda(), is_causal=causal, simthreshd1=0.6,
+                                           cdfthreshd=cdf, return_sparsity=True)
+    _status_ok()
+    assert abs(sp - sp_ref) < 1e-6
+    _check(o, o_ref)
+
+
 def test_nhd_layout_and_per_head_knobs():
     import spargeattn_b200 as S
     B, H, N, D = 1, 3, 700, 64

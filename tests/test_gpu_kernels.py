@@ -120,6 +120,24 @@ def test_select_mask_and_lut_bit_exact(shape, dtype, causal, sink, topk):
     assert torch.equal(lut.cpu(), pr["lut"])
 
 
+@pytest.mark.parametrize("shape", [(1, 2, 640, 64), (2, 3, 1000, 128), (1, 2, 4096, 64), (1, 1, 8192, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal,cdf", [(False, 0.9), (True, 0.98), (False, 0.5), (False, 1.5), (False, 0.0)])
+def test_select_cdf_mode_bit_exact(shape, dtype, causal, cdf):
+    ops = _ops()
+    B, H, N, D = shape
+    q, k = _rand_qk(B, H, N, D, dtype, 8)
+    km = O.k_mean(k)
+    thr = torch.full((H,), 0.3)
+    cdf_t = torch.full((H,), cdf)
+    pr = O.predictor(q, k, km, causal, thr, cdf_t, None, False)
+    lut, valid, mask = ops.select_blocks(pr["pq"].cuda(), pr["pk"].cuda(), pr["sim_q"].to(torch.uint8).cuda(),
+                                         pr["sim_k"].to(torch.uint8).cuda(), None, cdf_t.cuda(), causal, False,
+                                         want_mask=True)
+    assert torch.equal(mask.cpu().bool(), pr["map"]), f"{(mask.cpu().bool() != pr['map']).sum().item()} blocks differ"
+    assert torch.equal(valid.cpu(), pr["valid"]) and torch.equal(lut.cpu(), pr["lut"])
+
+
 def test_select_ties_go_to_lower_index():
     """Identical pooled keys give identical probabilities: the stable order must keep the lowest indices."""
     ops = _ops()
