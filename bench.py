@@ -26,6 +26,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "dense_equivalent_attention_throughput_topk0.5"
+PVTHRESHD = 50.0
 UNIT = "TOPS"
 NOMINAL_8BIT_TOPS = 4500.0
 
@@ -33,10 +34,11 @@ NOMINAL_8BIT_TOPS = 4500.0
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", type=int, default=2, help="index into spargeattn_b200.synthetic.WORKLOADS")
     ap.add_argument("--topk", type=float, default=None)
+    ap.add_argument("--pvthreshd", type=float, default=50.0, help="PV-skip threshold passed to the API (default 50)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="device-resident arm only (for profiler runs)")
@@ -63,7 +65,7 @@ def config_dict(idx, w, topk, n_gpus, ulysses=False):
                 f"{H // n_gpus} heads per rank and back (strong scaling)") if ulysses else \
         f"{n_gpus} x full head set (weak scaling, no collective)"
     return {"workload": f"cfg{idx}:{w['name']} B={B} H={H} N={N} D={D} bf16 {'causal' if w['causal'] else 'non-causal'} "
-                        f"topk={topk} pvthreshd=50 (API default)",
+                        f"topk={topk} pvthreshd={PVTHRESHD:g}",
             "per_gpu_heads": H // n_gpus if ulysses else H, "sharding": sharding,
             "l2_policy": "inputs larger than L2 (q,k,v = %.0f MB per rank)" % (3 * B * H * N * D * 2 / 1e6)}
 
@@ -87,7 +89,7 @@ class ClockSampler:
                     self.samples.append(parts)
             except Exception:
                 pass
-            self.stop.wait(0.2)
+            self.stop.wait(0.05)
 
     def __enter__(self):
         self.th = threading.Thread(target=self._run, daemon=True)
@@ -165,7 +167,9 @@ def run_reference(args, idx, w, topk):
 
 # ------------------------------------------------------------------------------------------ GPU arm
 def main():
+    global PVTHRESHD
     args = parse()
+    PVTHRESHD = args.pvthreshd
     from spargeattn_b200 import synthetic
     idx = args.workload
     w = synthetic.WORKLOADS[idx]
@@ -202,9 +206,10 @@ def main():
         assert N % world == 0 and H % world == 0
         n_loc = N // world
         q, k, v = (t[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous() for t in (q, k, v))
-        api = lambda a, b, c: ulysses_attention(a, b, c, topk=topk, is_causal=causal)
+        api = lambda a, b, c: ulysses_attention(a, b, c, topk=topk, is_causal=causal, pvthreshd=args.pvthreshd)
     else:
-        api = lambda a, b, c: S.spas_sage2_attn_meansim_topk_cuda(a, b, c, topk=topk, is_causal=causal)
+        api = lambda a, b, c: S.spas_sage2_attn_meansim_topk_cuda(a, b, c, topk=topk, is_causal=causal,
+                                                                 pvthreshd=args.pvthreshd)
 
     def barrier():
         torch.cuda.synchronize()
@@ -230,13 +235,15 @@ def main():
     # ---- device-resident arm
     for _ in range(args.warmup):
         o = api(q, k, v)
-    with ClockSampler(local) as clk:
-        ms_step = timed(lambda: api(q, k, v), args.steps)
+    clk = ClockSampler(local)
+    clk.__enter__()
+    ms_step = timed(lambda: api(q, k, v), args.steps)
     ops.check_device_status(dev)
     total_ops = dense_equiv_ops(B, H, N, D, causal) * (1 if ulysses else world)
     value = total_ops / (ms_step * 1e-3) / 1e12
 
     if args.quick:
+        clk.__exit__()
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                               "warmup": args.warmup, "ms_per_step": ms_step, "quick": True,
@@ -260,6 +267,7 @@ def main():
         e2e_step()
     e2e_steps = max(3, min(args.steps, 10))
     ms_e2e = timed(e2e_step, e2e_steps)
+    clk.__exit__()
     e2e_value = total_ops / (ms_e2e * 1e-3) / 1e12
     in_bytes, out_bytes = 3 * q.numel() * 2, q.numel() * 2
 
@@ -277,7 +285,7 @@ def main():
         qc, kc, vc = core._prologue(q, k, v, "HND")
         thr = core.hyperparameter_check(-0.1, H, dev)
         tk = core.hyperparameter_check(topk, H, dev)
-        pv = core._pv_threshold_tensor(50, H, dev)      # the API default: PV-skip test compiled out
+        pv = core._pv_threshold_tensor(args.pvthreshd, H, dev)   # None for the API default (test compiled out)
         reps = max(5, min(args.steps, 20))
 
         def t_kernel(fn):
@@ -319,6 +327,13 @@ def main():
         peak8 = 2.0 * bf16_peak
         kernels["attn"] = {"ms": t_attn, "active_TOPS": achieved, "live_blocks": live,
                            "density": live / float(B * H * nq * nk)}
+        # comparator: the same kernel with every block live = a dense INT8/FP8 attention of this shape
+        ones = torch.ones(B, H, nq, nk, dtype=torch.uint8, device=dev)
+        lut_d, valid_d = ops.mask_to_lut(ones)
+        t_dense = t_kernel(lambda: ops.attn_fwd(q8, k8, v8, lut_d, valid_d, pv, qs, ks, vs, D ** -0.5, False, qc.dtype, out))
+        kernels["attn_dense_mask"] = {"ms": t_dense, "dense_TOPS": dense_equiv_ops(B, H, N, D, False) / (t_dense * 1e-3) / 1e12,
+                                      "sparse_kernel_speedup": t_dense / t_attn}
+        del ones, lut_d, valid_d
         for kname in ("k_mean", "pool_quant_q", "pool_quant_k", "select", "quant_v"):
             kernels[kname]["frac_of_hbm_peak"] = kernels[kname]["GBps"] / hbm_peak
         roofline = {"kernel": "attn_kernel (tcgen05 INT8 QK^T + FP8 PV)", "bound": "tensor", "achieved": achieved,

@@ -69,8 +69,13 @@ __device__ __forceinline__ float key_value<__nv_bfloat16>(uint32_t k) {
 // pooled K rows it streams are shared through L1. Everything is warp-synchronous (shuffles and
 // ballots), there is no block-wide barrier.
 // dynamic smem: [32][D*2+16] byte staging tile of pooled K rows (shared by the CTA's rows), then per
-// row: double e[nk] | uint32 key[nk] | int idx[nk] (also the fp32 scores) | float q[D]
+// row: int idx[nk] (first the fp32 scores) | float q[D] | uint16 key[nk].  The fp64 exponentials are
+// evaluated twice (once for the sum, once for the probabilities) instead of being stored: at long
+// sequences shared memory per row, not arithmetic, limits how many rows an SM can hold.
 constexpr int kSelRowsPerCta = 4;
+__host__ __device__ inline size_t select_row_bytes(int nk, int D) {
+  return (((size_t)nk * 4 + (size_t)D * 4 + (size_t)nk * 2) + 15) / 16 * 16;
+}
 
 __device__ __forceinline__ int warp_sum_int(int x) {
 #pragma unroll
@@ -90,13 +95,12 @@ select_kernel(const T* __restrict__ pq, const T* __restrict__ pk, const uint8_t*
   const bool active = warp < rows_per_cta && qi < nq;       // inactive warps still help to stage K tiles
   constexpr int kTileRowBytes = D * (int)sizeof(T) + 16;   // 16-byte pad: conflict-free 128-bit reads, one row per lane
   unsigned char* s_tile = smem_raw;
-  const size_t row_bytes = (size_t)nk * 16 + D * sizeof(float);
+  const size_t row_bytes = select_row_bytes(nk, D);
   unsigned char* base = smem_raw + 32 * kTileRowBytes + (size_t)(active ? warp : 0) * row_bytes;
-  double* s_e = reinterpret_cast<double*>(base);
-  uint32_t* s_key = reinterpret_cast<uint32_t*>(s_e + nk);
-  int* s_idx = reinterpret_cast<int*>(s_key + nk);
+  int* s_idx = reinterpret_cast<int*>(base);
   float* s_s = reinterpret_cast<float*>(s_idx);            // scores share storage with the index list
   float* s_q = reinterpret_cast<float*>(s_idx + nk);
+  uint16_t* s_key = reinterpret_cast<uint16_t*>(s_q + D);
   const int k_limit = is_causal ? min(nk, (qi + 1) * (kBlockQ / kBlockK)) : nk;   // causal: k < (q+1)*2
 
   if (active)
@@ -145,14 +149,15 @@ select_kernel(const T* __restrict__ pq, const T* __restrict__ pk, const uint8_t*
   double Z = 0.0;
   for (int j = lane; j < nk; j += 32) {
     const float sc = s_s[j];
-    const double e = (sc == -INFINITY) ? 0.0 : exp((double)sc - (double)m);
-    s_e[j] = e;
-    Z += e;
+    Z += (sc == -INFINITY) ? 0.0 : exp((double)sc - (double)m);
   }
   Z = warp_sum(Z);
   const bool empty_row = (m == -INFINITY);
-  for (int j = lane; j < nk; j += 32)
-    s_key[j] = empty_row ? 0u : key_bits<T>(Elem<T>::from_float((float)(s_e[j] / Z)));
+  for (int j = lane; j < nk; j += 32) {
+    const float sc = s_s[j];
+    const double e = (sc == -INFINITY) ? 0.0 : exp((double)sc - (double)m);
+    s_key[j] = empty_row ? (uint16_t)0 : (uint16_t)key_bits<T>(Elem<T>::from_float((float)(e / Z)));
+  }
   __syncwarp();
 
   // ---- how many blocks to select
@@ -297,7 +302,7 @@ template <typename T, int D>
 static int launch_select(const void* pq, const void* pk, const uint8_t* sim_q, const uint8_t* sim_k, const float* topk,
                          const float* cdf, uint8_t* mask, int32_t* lut, int32_t* valid, int BH, int H, int nq, int nk,
                          int causal, int sink, cudaStream_t st) {
-  const size_t row_bytes = (size_t)nk * 16 + D * sizeof(float);
+  const size_t row_bytes = select_row_bytes(nk, D);
   const size_t tile_bytes = 32 * (D * sizeof(T) + 16);
   const size_t budget = 200 * 1024 - tile_bytes;
   if (row_bytes > budget) return SPARGE_ERR_TOO_LARGE;
