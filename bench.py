@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--pvthreshd", type=float, default=50.0, help="PV-skip threshold passed to the API (default 50)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-heads-per-chunk", type=int, default=2)
     ap.add_argument("--quick", action="store_true", help="device-resident arm only (for profiler runs)")
     return ap.parse_args()
 
@@ -255,13 +256,21 @@ def main():
     # ---- end-to-end arm: pinned host buffers in, host buffer out, copies inside the timed region
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty_like(hq).pin_memory()
-    dq, dk, dv = (torch.empty_like(t) for t in (q, k, v))
+    if ulysses:
+        dq, dk, dv = (torch.empty_like(t) for t in (q, k, v))
 
-    def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
-        ho.copy_(api(dq, dk, dv), non_blocking=True)
+        def e2e_step():
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            ho.copy_(api(dq, dk, dv), non_blocking=True)
+    else:
+        # the library's host-buffer front end: head chunks pipelined over upload / compute / download streams
+        from spargeattn_b200.host import spas_sage2_attn_meansim_topk_host
+
+        def e2e_step():
+            spas_sage2_attn_meansim_topk_host(hq, hk, hv, out=ho, device=dev, heads_per_chunk=args.e2e_heads_per_chunk,
+                                              topk=topk, is_causal=causal, pvthreshd=args.pvthreshd)
 
     for _ in range(2):
         e2e_step()

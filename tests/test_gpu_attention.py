@@ -148,3 +148,18 @@ def test_linearity_in_v():
     o2 = S.spas_sage2_attn_meansim_topk_cuda(q.cuda(), k.cuda(), (v * 2).cuda(), topk=0.5)
     _status_ok()
     assert torch.allclose(o2.float(), 2 * o1.float(), rtol=2e-3, atol=1e-4)
+
+
+def test_host_front_end_matches_device_call():
+    """Pipelined host-buffer entry point: same bytes as one call on device tensors."""
+    import spargeattn_b200 as S
+    from spargeattn_b200.host import spas_sage2_attn_meansim_topk_host
+    B, H, N, D = 2, 5, 900, 64
+    q, k, v = _inputs(B, H, N, D, torch.bfloat16, 18)
+    topk = torch.tensor([0.3, 0.4, 0.5, 0.6, 0.7])
+    ref = S.spas_sage2_attn_meansim_topk_cuda(q.cuda(), k.cuda(), v.cuda(), topk=topk)
+    for hpc in (1, 2, 5):
+        out = spas_sage2_attn_meansim_topk_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), heads_per_chunk=hpc, topk=topk)
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref.cpu())
+    _status_ok()
