@@ -121,6 +121,13 @@ int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v
                     const float* v_scale, int32_t* dev_status, int B, int H, int N, int D, int out_dtype,
                     int is_causal, float sm_scale, sparge_stream_t stream);
 
+/* Failure-detection self test: launches one warp that waits on a barrier nobody signals, bounded by
+ * slices x slice_ns nanoseconds (at most 0.1 s in total), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into
+ * *dev_status when the bounded wait gives up -- the same code path that sparge_attn_fwd takes if a
+ * producer / MMA / softmax hand-off ever stalls. The kernel then exits normally; the context stays usable.
+ * The reference has no counterpart (its sm90 kernel spins without a limit, qk_int_sv_f8_cuda_sm90.cuh:117-132). */
+int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int slice_ns, unsigned int slices, sparge_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,6 +29,7 @@ SIGNATURES = {
     "sparge_select": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "sparge_mask_to_lut": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p]),
     "sparge_quant_v": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "sparge_selftest_wait_expiry": (_i, [_p, ctypes.c_uint, ctypes.c_uint, _p]),
     "sparge_attn_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p]),
 }
 for _name, (_res, _args) in SIGNATURES.items():

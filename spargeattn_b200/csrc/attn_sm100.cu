@@ -77,7 +77,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   __shared__ float s_delta[2][4];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qi = blockIdx.x, bh = blockIdx.y, h = bh % H;
+  // Query blocks are issued last-first: under a causal mask the late rows hold the most live blocks,
+  // and starting the longest rows first keeps the final wave short.
+  const int qi = (int)gridDim.x - 1 - (int)blockIdx.x, bh = blockIdx.y, h = bh % H;
   const size_t row_id = (size_t)bh * nq + qi;
   int cnt = valid[row_id];
   cnt = min(cnt, nk);
@@ -279,35 +281,40 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         const float dcta = fmaxf(fmaxf(s_delta[b][0], s_delta[b][1]), fmaxf(s_delta[b][2], s_delta[b][3]));
         skip = (dcta + thr <= 0.f);
       }
-      if (n > 0) {
-        const float alpha = ex2_approx(m - m_new);
-        if (__any_sync(0xffffffffu, m_new > m)) {   // some row of this warp raised its maximum: rescale O
-          // PV(n-1) must have landed before O is touched. Blocks <= n-2 are known complete (the commit
-          // behind s_full(n) covers them), so a parity wait on phase n-1 cannot alias even though
-          // iterations without a rescale skip this wait.
-          ok = mbar_wait(&bar_o_done, (n - 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
+      // Rescaling of the running output is deferred until after the exponentials: by then PV(n-1) has
+      // normally retired, so the wait below does not stall. The wait itself is unconditional: a parity
+      // wait only tells phases apart if every phase of the barrier is observed in order.
+      const float alpha = (n > 0) ? ex2_approx(m - m_new) : 0.f;
+      const bool need_rescale = (n > 0) && __any_sync(0xffffffffu, m_new > m);
+      auto settle_output = [&]() -> bool {
+        if (n > 0) {
+          if (!mbar_wait(&bar_o_done, (n - 1) & 1)) return false;
+          if (need_rescale) {   // some row of this warp raised its maximum
+            tc_fence_after();
 #pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t ov[32];
-            tmem_ld32(tO + tlane + c0, ov);
-            tmem_wait_ld();
-            const float2 al2 = make_float2(alpha, alpha);
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t ov[32];
+              tmem_ld32(tO + tlane + c0, ov);
+              tmem_wait_ld();
+              const float2 al2 = make_float2(alpha, alpha);
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float2 r2 = __fmul2_rn(make_float2(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1])), al2);
-              ov[i] = __float_as_uint(r2.x);
-              ov[i + 1] = __float_as_uint(r2.y);
+              for (int i = 0; i < 32; i += 2) {
+                const float2 r2 = __fmul2_rn(make_float2(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1])), al2);
+                ov[i] = __float_as_uint(r2.x);
+                ov[i + 1] = __float_as_uint(r2.y);
+              }
+              tmem_st32(tO + tlane + c0, ov);
             }
-            tmem_st32(tO + tlane + c0, ov);
+            tmem_wait_st();
           }
-          tmem_wait_st();
         }
-        d *= alpha;
-      }
+        return true;
+      };
+      d *= alpha;
       m = m_new;
       if (skip) {
+        ok = settle_output();
+        if (!ok) break;
         if (tid == 0) s_skip[b] = 1;
         tc_fence_before();
         __syncwarp();
@@ -358,6 +365,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         }
       }
       d += sum;
+      ok = settle_output();
+      if (!ok) break;
       tmem_st16(tS, pr);
       tmem_wait_st();
       if (PV_SKIP && tid == 0) s_skip[b] = 0;
@@ -443,7 +452,28 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   return launch_status();
 }
 
+// One warp waits on an mbarrier that nobody arrives at, with a caller-chosen short limit, and reports
+// the expiry through the same status word and code path as the attention kernel's bounded waits.
+__global__ void wait_expiry_selftest_kernel(int32_t* dev_status, uint32_t slice_ns, uint32_t slices) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const bool ok = mbar_wait(&bar, 0, slice_ns, slices);
+  if (!ok && threadIdx.x == 0) report(dev_status, SPARGE_DEV_TIMEOUT_SOFTMAX);
+}
+
 }  // namespace sparge
+
+extern "C" int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int slice_ns, unsigned int slices,
+                                           sparge_stream_t stream) {
+  if (!dev_status) return SPARGE_ERR_NULL;
+  if (slice_ns == 0 || slices == 0 || (unsigned long long)slice_ns * slices > 100000000ull) return SPARGE_ERR_INVALID_ARG;
+  sparge::wait_expiry_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(dev_status, slice_ns, slices);
+  return sparge::launch_status();
+}
 
 extern "C" int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
                                const int32_t* lut, const int32_t* valid, const float* pvthreshd, const float* q_scale,

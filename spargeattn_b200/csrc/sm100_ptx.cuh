@@ -59,7 +59,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // kWaitSlices slices bound the total wait to about one second.
 constexpr uint32_t kWaitSliceNs = 1000000u;   // 1 ms
 constexpr uint32_t kWaitSlices = 1000u;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t slice_ns = kWaitSliceNs,
+                                          uint32_t slices = kWaitSlices) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
@@ -76,7 +77,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
       "selp.u32 %0, 1, 0, P1;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitSliceNs), "r"(kWaitSlices)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(slice_ns), "r"(slices)
       : "memory");
   return ok != 0;
 }
