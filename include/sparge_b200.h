@@ -121,6 +121,26 @@ int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v
                     const float* v_scale, int32_t* dev_status, int B, int H, int N, int D, int out_dtype,
                     int is_causal, float sm_scale, sparge_stream_t stream);
 
+/* Strided variants: the 16-bit inputs (and the attention output) may be any [B,H,N,D] view whose last
+ * dimension is contiguous, given by element strides of the batch, head and token dimensions -- for
+ * example the "NHD" tensors [B,N,H,D] that attention processors produce (stride_h = D, stride_n = H*D)
+ * -- so that no permuted copy is made before or after the path (the reference's prologue copies q, k, v,
+ * spas_sage_attn/core.py:107-117, and its callers copy again, inference_examples/modify_model/
+ * modify_wan.py:116-118). Base pointers must be 16-byte aligned and strides multiples of 8 elements.
+ * The quantised / pooled outputs are always contiguous HND. */
+int sparge_k_mean_strided(const void* k, void* km, void* scratch, int B, int H, int N, int D, int dtype,
+                          long long stride_b, long long stride_h, long long stride_n, sparge_stream_t stream);
+int sparge_pool_quant_strided(const void* x, const void* km, const float* simthreshd1, void* pool, uint8_t* sim,
+                              int8_t* x_int8, float* scale, int B, int H, int N, int D, int block, int dtype,
+                              long long stride_b, long long stride_h, long long stride_n, sparge_stream_t stream);
+int sparge_quant_v_strided(const void* v, uint8_t* v8, float* v_scale, int B, int H, int N, int D, int dtype,
+                           long long stride_b, long long stride_h, long long stride_n, sparge_stream_t stream);
+int sparge_attn_fwd_strided(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o, const int32_t* lut,
+                            const int32_t* valid, const float* pvthreshd, const float* q_scale, const float* k_scale,
+                            const float* v_scale, int32_t* dev_status, int B, int H, int N, int D, int out_dtype,
+                            int is_causal, float sm_scale, long long o_stride_b, long long o_stride_h,
+                            long long o_stride_n, sparge_stream_t stream);
+
 /* Failure-detection self test: launches one warp that waits on a barrier nobody signals, bounded by
  * slices x slice_ns nanoseconds (at most 0.1 s in total), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into
  * *dev_status when the bounded wait gives up -- the same code path that sparge_attn_fwd takes if a

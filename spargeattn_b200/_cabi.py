@@ -16,7 +16,7 @@ if not os.path.exists(LIB_PATH):
 
 lib = ctypes.CDLL(LIB_PATH)
 
-_p, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+_p, _i, _f, _sz, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_longlong
 
 # name -> (restype, argtypes); must list every symbol of include/sparge_b200.h
 SIGNATURES = {
@@ -29,6 +29,10 @@ SIGNATURES = {
     "sparge_select": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "sparge_mask_to_lut": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p]),
     "sparge_quant_v": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "sparge_k_mean_strided": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _ll, _ll, _ll, _p]),
+    "sparge_pool_quant_strided": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _p]),
+    "sparge_quant_v_strided": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _ll, _ll, _ll, _p]),
+    "sparge_attn_fwd_strided": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _ll, _ll, _ll, _p]),
     "sparge_selftest_wait_expiry": (_i, [_p, ctypes.c_uint, ctypes.c_uint, _p]),
     "sparge_attn_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p]),
 }

@@ -21,10 +21,20 @@ from . import ops
 SAGE2_TOKEN_LEVEL_CAUSAL = False
 
 
+_knob_cache = {}
+
+
 def hyperparameter_check(hyper, H, device):
-    """spas_sage_attn/utils.py:38-50."""
+    """spas_sage_attn/utils.py:38-50. Scalar knobs are materialised once per (value, H, device) and reused:
+    the tensors are read-only inputs of the kernels, and small calls are otherwise launch-bound."""
     if type(hyper) == float or type(hyper) == int:
-        hyper = torch.full((H,), float(hyper), device=device)
+        key = (float(hyper), H, str(device))
+        cached = _knob_cache.get(key)
+        if cached is None:
+            cached = torch.full((H,), float(hyper), device=device, dtype=torch.float32)
+            if len(_knob_cache) < 256:
+                _knob_cache[key] = cached
+        return cached
     elif isinstance(hyper, torch.Tensor):
         assert len(hyper.shape) <= 1, "Hyperparameter tensor must be 1D"
         if len(hyper.shape) == 0:
@@ -58,14 +68,26 @@ def _prologue(q, k, v, tensor_layout):
     assert q.size(-2) >= 128, "seq_len should be not less than 128."
     torch.cuda.set_device(v.device)
     dtype = q.dtype
-    if dtype == torch.float32 or dtype == torch.float16:
-        q, k = q.contiguous().to(torch.float16), k.contiguous().to(torch.float16)
-    else:
-        q, k = q.contiguous().to(torch.bfloat16), k.contiguous().to(torch.bfloat16)
-    v = v.contiguous()
-    if v.dtype not in (torch.float16, torch.bfloat16):
-        v = v.to(torch.float16)
+    qk_dtype = torch.float16 if dtype in (torch.float32, torch.float16) else torch.bfloat16
+
+    def prep(t, want):
+        # The kernels read any [B,H,N,D] view with a contiguous last dimension in place (an "NHD" tensor seen
+        # through transpose is such a view); only other layouts / dtypes are copied, as the reference always does.
+        if want is not None and t.dtype != want:
+            t = t.to(want)
+        return t if ops.strided_ok(t) else t.contiguous()
+
+    q, k = prep(q, qk_dtype), prep(k, qk_dtype)
+    v = prep(v, None if v.dtype in (torch.float16, torch.bfloat16) else torch.float16)
     return q, k, v
+
+
+def _empty_like_layout(q):
+    """Output buffer [B,H,N,D] in q's memory format (HND-contiguous, or NHD storage seen through a transpose)."""
+    B, H, N, D = q.shape
+    if q.stride(1) == D and q.stride(2) == H * D and q.stride(0) == N * H * D:
+        return torch.empty(B, N, H, D, dtype=q.dtype, device=q.device).transpose(1, 2)
+    return torch.empty(B, H, N, D, dtype=q.dtype, device=q.device)
 
 
 def get_block_map_meansim_fuse_quant(q, k, km=None, is_causal=False, BLKQ=128, BLKK=64, simthreshd1=0.1,
@@ -125,7 +147,7 @@ def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthre
     pvthreshd = _pv_threshold_tensor(pvthreshd, q.size(-3), q.device)
     v_fp8, v_scale = ops.quant_v(v)
     o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale,
-                     kernel_causal, q.dtype)
+                     kernel_causal, q.dtype, out=_empty_like_layout(q))
     if tensor_layout == 'NHD':
         o = o.transpose(-2, -3)
     if return_sparsity:
@@ -171,7 +193,7 @@ def block_sparse_sage2_attn_cuda(q, k, v, mask_id=None, dropout_p=0.0, scale=Non
     pvthreshd = _pv_threshold_tensor(pvthreshd, q.size(-3), q.device)
     v_fp8, v_scale = ops.quant_v(v)
     o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale, False,
-                     q.dtype)
+                     q.dtype, out=_empty_like_layout(q))
     if tensor_layout == 'NHD':
         o = o.transpose(-2, -3)
     if return_sparsity:

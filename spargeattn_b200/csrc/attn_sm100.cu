@@ -62,7 +62,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
             const __grid_constant__ CUtensorMap tmap_v, OutT* __restrict__ o, const int32_t* __restrict__ lut,
             const int32_t* __restrict__ valid, const float* __restrict__ pvthr, const float* __restrict__ q_scale,
             const float* __restrict__ k_scale, const float* __restrict__ v_scale, int32_t* dev_status, int N, int H,
-            int nq, int nk, float sm_scale_log2, int one) {
+            int nq, int nk, float sm_scale_log2, int one, long long osb, long long osh, long long osn) {
   using Shape = AttnShape<D>;
   constexpr int STAGES = Shape::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -86,8 +86,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
 
   if (cnt <= 0) {   // no live block: defined output (zeros)
     const int rows = min(128, N - qi * 128);
-    uint4* dst = reinterpret_cast<uint4*>(o + ((size_t)bh * N + (size_t)qi * 128) * D);
-    for (int i = tid; i < rows * D * (int)sizeof(OutT) / 16; i += 192) dst[i] = make_uint4(0, 0, 0, 0);
+    constexpr int kChunks = D * (int)sizeof(OutT) / 16;
+    OutT* obase = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qi * 128 * osn;
+    for (int i = tid; i < rows * kChunks; i += 192)
+      reinterpret_cast<uint4*>(obase + (size_t)(i / kChunks) * osn)[i % kChunks] = make_uint4(0, 0, 0, 0);
     return;
   }
 
@@ -379,7 +381,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       tc_fence_after();
       const float inv = rcp_approx(d);
       const float* vs = v_scale + (size_t)bh * D;
-      OutT* orow = o + ((size_t)bh * N + qrow) * D;
+      OutT* orow = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qrow * osn;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t ov[32];
@@ -440,7 +442,8 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t r
 template <int D, bool CAUSAL, bool PV_SKIP, typename OutT>
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, const int32_t* lut,
                        const int32_t* valid, const float* pvthr, const float* qs, const float* ks, const float* vs,
-                       int32_t* status, int BH, int H, int N, float sm_scale_log2, cudaStream_t st) {
+                       int32_t* status, int BH, int H, int N, float sm_scale_log2, long long osb, long long osh,
+                       long long osn, cudaStream_t st) {
   auto kern = attn_kernel<D, CAUSAL, PV_SKIP, OutT>;
   constexpr int smem = AttnShape<D>::kSmemBytes;
   // function attributes are per device: set on every call (cheap) rather than caching
@@ -448,7 +451,7 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   const int nq = (N + 127) / 128, nk = (N + 63) / 64;
   kern<<<dim3(nq, BH), 192, smem, st>>>(tq, tk, tv, (OutT*)o, lut, valid, pvthr, qs, ks, vs, status, N, H, nq, nk,
-                                        sm_scale_log2, 1);
+                                        sm_scale_log2, 1, osb, osh, osn);
   return launch_status();
 }
 
@@ -475,16 +478,19 @@ extern "C" int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int sli
   return sparge::launch_status();
 }
 
-extern "C" int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
-                               const int32_t* lut, const int32_t* valid, const float* pvthreshd, const float* q_scale,
-                               const float* k_scale, const float* v_scale, int32_t* dev_status, int B, int H, int N,
-                               int D, int out_dtype, int is_causal, float sm_scale, sparge_stream_t stream) {
+extern "C" int sparge_attn_fwd_strided(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
+                                       const int32_t* lut, const int32_t* valid, const float* pvthreshd,
+                                       const float* q_scale, const float* k_scale, const float* v_scale,
+                                       int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
+                                       float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
+                                       sparge_stream_t stream) {
   using namespace sparge;
   if (!q_int8 || !k_int8 || !v8 || !o || !lut || !valid || !q_scale || !k_scale || !v_scale) return SPARGE_ERR_NULL;
   if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (out_dtype != SPARGE_F16 && out_dtype != SPARGE_BF16))
     return SPARGE_ERR_INVALID_ARG;
   if (!(sm_scale > 0.f)) return SPARGE_ERR_INVALID_ARG;
   if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;
+  if (!strides_ok(o, o_stride_b, o_stride_h, o_stride_n)) return SPARGE_ERR_INVALID_ARG;
   const int BH = B * H;
   const int N_pad = (N + 127) / 128 * 128;
   CUtensorMap tq, tk, tv;
@@ -494,7 +500,7 @@ extern "C" int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const
   const float sl2 = sm_scale * kLog2e;
   const bool causal = is_causal != 0, skip = pvthreshd != nullptr, bf = out_dtype == SPARGE_BF16;
 #define SPARGE_ATTN(DD, C, S, T) \
-  launch_attn<DD, C, S, T>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, BH, H, N, sl2, st)
+  launch_attn<DD, C, S, T>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, BH, H, N, sl2, o_stride_b, o_stride_h, o_stride_n, st)
 #define SPARGE_ATTN_T(DD, C, S) (bf ? SPARGE_ATTN(DD, C, S, __nv_bfloat16) : SPARGE_ATTN(DD, C, S, __half))
 #define SPARGE_ATTN_S(DD, C) (skip ? SPARGE_ATTN_T(DD, C, true) : SPARGE_ATTN_T(DD, C, false))
 #define SPARGE_ATTN_C(DD) (causal ? SPARGE_ATTN_S(DD, true) : SPARGE_ATTN_S(DD, false))
@@ -503,4 +509,12 @@ extern "C" int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const
 #undef SPARGE_ATTN_S
 #undef SPARGE_ATTN_T
 #undef SPARGE_ATTN
+}
+
+extern "C" int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
+                               const int32_t* lut, const int32_t* valid, const float* pvthreshd, const float* q_scale,
+                               const float* k_scale, const float* v_scale, int32_t* dev_status, int B, int H, int N,
+                               int D, int out_dtype, int is_causal, float sm_scale, sparge_stream_t stream) {
+  return sparge_attn_fwd_strided(q_int8, k_int8, v8, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, B, H,
+                                 N, D, out_dtype, is_causal, sm_scale, (long long)H * N * D, (long long)N * D, D, stream);
 }

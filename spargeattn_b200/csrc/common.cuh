@@ -43,6 +43,12 @@ __device__ __forceinline__ float warp_max(float x) {
   return x;
 }
 
+// Strided [B,H,N,D] views (D contiguous) are read with 128-bit loads: base and strides must keep 16-byte alignment.
+inline bool strides_ok(const void* base, long long sb, long long sh, long long sn) {
+  return (reinterpret_cast<uintptr_t>(base) % 16 == 0) && sb >= 0 && sh >= 0 && sn > 0 && sb % 8 == 0 && sh % 8 == 0 &&
+         sn % 8 == 0;
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SPARGE_OK : SPARGE_ERR_CUDA;

@@ -17,7 +17,8 @@ static __device__ __align__(256) double g_kmean_static_scratch[kStaticScratchDou
 
 // grid (chunks, B*H), 256 threads. Each thread owns 8 channels of every (256 / (D/8))-th row.
 template <typename T, int D>
-__global__ void __launch_bounds__(256) kmean_partial_kernel(const T* __restrict__ k, double* __restrict__ part, int N) {
+__global__ void __launch_bounds__(256) kmean_partial_kernel(const T* __restrict__ k, double* __restrict__ part, int N, int H,
+                                                            long long sb, long long sh, long long sn) {
   constexpr int TPR = D / 8;        // threads per row
   constexpr int RPP = 256 / TPR;    // rows per pass
   __shared__ double red[RPP][D];
@@ -25,12 +26,12 @@ __global__ void __launch_bounds__(256) kmean_partial_kernel(const T* __restrict_
   const int chunk = blockIdx.x, bh = blockIdx.y, chunks = gridDim.x;
   const int row_begin = chunk * kMeanRowsPerCta;
   const int row_end = min(N, row_begin + kMeanRowsPerCta);
-  const T* base = k + (size_t)bh * N * D;
+  const T* base = k + (size_t)(bh / H) * sb + (size_t)(bh % H) * sh;
   double acc[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = 0.0;
   for (int row = row_begin + r0; row < row_end; row += RPP) {
-    Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * D + cg * 8);
+    Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * sn + cg * 8);
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[i] += (double)Elem<T>::to_float(p.v[i]);
   }
@@ -55,9 +56,10 @@ __global__ void kmean_final_kernel(const double* __restrict__ part, T* __restric
 }
 
 template <typename T, int D>
-static int launch_kmean(const void* k, void* km, void* scratch, int BH, int N, cudaStream_t st) {
+static int launch_kmean(const void* k, void* km, void* scratch, int BH, int H, int N, long long sb, long long sh,
+                        long long sn, cudaStream_t st) {
   const int chunks = (N + kMeanRowsPerCta - 1) / kMeanRowsPerCta;
-  kmean_partial_kernel<T, D><<<dim3(chunks, BH), 256, 0, st>>>((const T*)k, (double*)scratch, N);
+  kmean_partial_kernel<T, D><<<dim3(chunks, BH), 256, 0, st>>>((const T*)k, (double*)scratch, N, H, sb, sh, sn);
   kmean_final_kernel<T, D><<<BH, D, 0, st>>>((const double*)scratch, (T*)km, N, chunks);
   return launch_status();
 }
@@ -70,19 +72,26 @@ extern "C" size_t sparge_k_mean_scratch_bytes(int B, int H, int N, int D) {
   return (size_t)B * H * chunks * D * sizeof(double);
 }
 
-extern "C" int sparge_k_mean(const void* k, void* km, void* scratch, int B, int H, int N, int D, int dtype,
-                             sparge_stream_t stream) {
+extern "C" int sparge_k_mean_strided(const void* k, void* km, void* scratch, int B, int H, int N, int D, int dtype,
+                                     long long stride_b, long long stride_h, long long stride_n,
+                                     sparge_stream_t stream) {
   using namespace sparge;
   if (!k || !km || !scratch) return SPARGE_ERR_NULL;
   if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (dtype != SPARGE_F16 && dtype != SPARGE_BF16))
     return SPARGE_ERR_INVALID_ARG;
   if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;
+  if (!strides_ok(k, stride_b, stride_h, stride_n)) return SPARGE_ERR_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const int BH = B * H;
-  if (dtype == SPARGE_F16)
-    return D == 64 ? launch_kmean<__half, 64>(k, km, scratch, BH, N, st) : launch_kmean<__half, 128>(k, km, scratch, BH, N, st);
-  return D == 64 ? launch_kmean<__nv_bfloat16, 64>(k, km, scratch, BH, N, st)
-                 : launch_kmean<__nv_bfloat16, 128>(k, km, scratch, BH, N, st);
+#define SPARGE_KM(T, DD) launch_kmean<T, DD>(k, km, scratch, BH, H, N, stride_b, stride_h, stride_n, st)
+  if (dtype == SPARGE_F16) return D == 64 ? SPARGE_KM(__half, 64) : SPARGE_KM(__half, 128);
+  return D == 64 ? SPARGE_KM(__nv_bfloat16, 64) : SPARGE_KM(__nv_bfloat16, 128);
+#undef SPARGE_KM
+}
+
+extern "C" int sparge_k_mean(const void* k, void* km, void* scratch, int B, int H, int N, int D, int dtype,
+                             sparge_stream_t stream) {
+  return sparge_k_mean_strided(k, km, scratch, B, H, N, D, dtype, (long long)H * N * D, (long long)N * D, D, stream);
 }
 
 extern "C" int sparge_k_mean_static(const void* k, void* km, int B, int H, int N, int D, int dtype,

@@ -41,7 +41,7 @@ template <typename T, int D, int BS, bool HAS_KM, bool WANT_POOL>
 __global__ void __launch_bounds__((BS / 8) * (D / 8))
 pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float* __restrict__ simthr,
                   T* __restrict__ pool, uint8_t* __restrict__ sim, int8_t* __restrict__ xq,
-                  float* __restrict__ scale_out, int N, int H, int nb) {
+                  float* __restrict__ scale_out, int N, int H, int nb, long long sb, long long sh, long long sn) {
   constexpr int TPR = D / 8;
   constexpr int G = BS / 8;
   constexpr int NT = G * TPR;
@@ -55,7 +55,7 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
   const int blk = blockIdx.x, bh = blockIdx.y;
   const int row_base = blk * BS;
   const int rows_here = min(BS, N - row_base);
-  const T* xb = x + ((size_t)bh * N + row_base) * D;
+  const T* xb = x + (size_t)(bh / H) * sb + (size_t)(bh % H) * sh + (size_t)row_base * sn;
 
   float kmv[8];
   if (HAS_KM) {
@@ -70,7 +70,7 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const int row = g * 8 + i;
-    raw[i] = (row < rows_here) ? *reinterpret_cast<const uint4*>(xb + (size_t)row * D + cg * 8) : make_uint4(0, 0, 0, 0);
+    raw[i] = (row < rows_here) ? *reinterpret_cast<const uint4*>(xb + (size_t)row * sn + cg * 8) : make_uint4(0, 0, 0, 0);
   }
 
   float amax = 0.f;
@@ -194,13 +194,13 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
 
 template <typename T, int D, int BS>
 static int launch_pq(const void* x, const void* km, const float* thr, void* pool, uint8_t* sim, int8_t* xq, float* sc,
-                     int BH, int H, int N, cudaStream_t st) {
+                     int BH, int H, int N, long long sb, long long sh, long long sn, cudaStream_t st) {
   const int nb = (N + BS - 1) / BS;
   dim3 grid(nb, BH);
   const bool has_km = km != nullptr, want = thr != nullptr;
 #define SPARGE_PQ(KM, WP)                                                                                         \
   pool_quant_kernel<T, D, BS, KM, WP><<<grid, (BS / 8) * (D / 8), 0, st>>>((const T*)x, (const T*)km, thr, (T*)pool, sim, xq, sc, \
-                                                            N, H, nb)
+                                                            N, H, nb, sb, sh, sn)
   if (has_km && want) SPARGE_PQ(true, true);
   else if (has_km) SPARGE_PQ(true, false);
   else if (want) SPARGE_PQ(false, true);
@@ -211,18 +211,19 @@ static int launch_pq(const void* x, const void* km, const float* thr, void* pool
 
 template <typename T>
 static int dispatch_pq(const void* x, const void* km, const float* thr, void* pool, uint8_t* sim, int8_t* xq, float* sc,
-                       int BH, int H, int N, int D, int block, cudaStream_t st) {
-  if (D == 64 && block == 128) return launch_pq<T, 64, 128>(x, km, thr, pool, sim, xq, sc, BH, H, N, st);
-  if (D == 64 && block == 64) return launch_pq<T, 64, 64>(x, km, thr, pool, sim, xq, sc, BH, H, N, st);
-  if (D == 128 && block == 128) return launch_pq<T, 128, 128>(x, km, thr, pool, sim, xq, sc, BH, H, N, st);
-  return launch_pq<T, 128, 64>(x, km, thr, pool, sim, xq, sc, BH, H, N, st);
+                       int BH, int H, int N, int D, int block, long long sb, long long sh, long long sn, cudaStream_t st) {
+  if (D == 64 && block == 128) return launch_pq<T, 64, 128>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
+  if (D == 64 && block == 64) return launch_pq<T, 64, 64>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
+  if (D == 128 && block == 128) return launch_pq<T, 128, 128>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
+  return launch_pq<T, 128, 64>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
 }
 
 }  // namespace sparge
 
-extern "C" int sparge_pool_quant(const void* x, const void* km, const float* simthreshd1, void* pool, uint8_t* sim,
-                                 int8_t* x_int8, float* scale, int B, int H, int N, int D, int block, int dtype,
-                                 sparge_stream_t stream) {
+extern "C" int sparge_pool_quant_strided(const void* x, const void* km, const float* simthreshd1, void* pool,
+                                         uint8_t* sim, int8_t* x_int8, float* scale, int B, int H, int N, int D,
+                                         int block, int dtype, long long stride_b, long long stride_h,
+                                         long long stride_n, sparge_stream_t stream) {
   using namespace sparge;
   if (!x || !x_int8 || !scale) return SPARGE_ERR_NULL;
   if (simthreshd1 && (!pool || !sim)) return SPARGE_ERR_NULL;
@@ -230,8 +231,18 @@ extern "C" int sparge_pool_quant(const void* x, const void* km, const float* sim
       (dtype != SPARGE_F16 && dtype != SPARGE_BF16))
     return SPARGE_ERR_INVALID_ARG;
   if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;
+  if (!strides_ok(x, stride_b, stride_h, stride_n)) return SPARGE_ERR_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == SPARGE_F16)
-    return dispatch_pq<__half>(x, km, simthreshd1, pool, sim, x_int8, scale, B * H, H, N, D, block, st);
-  return dispatch_pq<__nv_bfloat16>(x, km, simthreshd1, pool, sim, x_int8, scale, B * H, H, N, D, block, st);
+    return dispatch_pq<__half>(x, km, simthreshd1, pool, sim, x_int8, scale, B * H, H, N, D, block, stride_b, stride_h,
+                               stride_n, st);
+  return dispatch_pq<__nv_bfloat16>(x, km, simthreshd1, pool, sim, x_int8, scale, B * H, H, N, D, block, stride_b,
+                                    stride_h, stride_n, st);
+}
+
+extern "C" int sparge_pool_quant(const void* x, const void* km, const float* simthreshd1, void* pool, uint8_t* sim,
+                                 int8_t* x_int8, float* scale, int B, int H, int N, int D, int block, int dtype,
+                                 sparge_stream_t stream) {
+  return sparge_pool_quant_strided(x, km, simthreshd1, pool, sim, x_int8, scale, B, H, N, D, block, dtype,
+                                   (long long)H * N * D, (long long)N * D, D, stream);
 }

@@ -24,18 +24,19 @@ __device__ __forceinline__ float to_f16_value<__nv_bfloat16>(__nv_bfloat16 v) {
 
 // grid (chunks, B*H), 256 threads. amax accumulates as the bit pattern of a non-negative float.
 template <typename T, int D>
-__global__ void __launch_bounds__(256) v_amax_kernel(const T* __restrict__ v, unsigned int* __restrict__ amax_bits, int N) {
+__global__ void __launch_bounds__(256) v_amax_kernel(const T* __restrict__ v, unsigned int* __restrict__ amax_bits, int N, int H,
+                                                     long long sb, long long sh, long long sn) {
   constexpr int TPR = D / 8, RPP = 256 / TPR;
   __shared__ float red[RPP][D];
   const int tid = threadIdx.x, cg = tid % TPR, r0 = tid / TPR;
   const int bh = blockIdx.y;
   const int row_begin = blockIdx.x * kVRowsPerCta, row_end = min(N, row_begin + kVRowsPerCta);
-  const T* base = v + (size_t)bh * N * D;
+  const T* base = v + (size_t)(bh / H) * sb + (size_t)(bh % H) * sh;
   float mx[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) mx[i] = 0.f;
   for (int row = row_begin + r0; row < row_end; row += RPP) {
-    Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * D + cg * 8);
+    Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * sn + cg * 8);
 #pragma unroll
     for (int i = 0; i < 8; i++) mx[i] = fmaxf(mx[i], fabsf(to_f16_value<T>(p.v[i])));
   }
@@ -53,7 +54,8 @@ __global__ void __launch_bounds__(256) v_amax_kernel(const T* __restrict__ v, un
 // grid (ceil(N_pad / rows), B*H), 256 threads.
 template <typename T, int D>
 __global__ void __launch_bounds__(256) v_quant_kernel(const T* __restrict__ v, const float* __restrict__ amax,
-                                                      uint8_t* __restrict__ v8, int N, int N_pad) {
+                                                      uint8_t* __restrict__ v8, int N, int N_pad, int H,
+                                                      long long sb, long long sh, long long sn) {
   constexpr int TPR = D / 8, RPP = 256 / TPR;
   const int tid = threadIdx.x, cg = tid % TPR, r0 = tid / TPR;
   const int bh = blockIdx.y;
@@ -64,12 +66,12 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const T* __restrict__ v, c
     const float a = amax[(size_t)bh * D + cg * 8 + i];
     r[i] = a > 0.f ? __fdiv_rn(kVScaleMax, a) : 0.f;
   }
-  const T* base = v + (size_t)bh * N * D;
+  const T* base = v + (size_t)(bh / H) * sb + (size_t)(bh % H) * sh;
   uint8_t* out = v8 + (size_t)bh * N_pad * D;
   for (int row = row_begin + r0; row < row_end; row += RPP) {
     uint2 w = make_uint2(0u, 0u);
     if (row < N) {
-      Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * D + cg * 8);
+      Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * sn + cg * 8);
       float f[8];
 #pragma unroll
       for (int i = 0; i < 8; i++) f[i] = __fmul_rn(to_f16_value<T>(p.v[i]), r[i]);
@@ -86,28 +88,36 @@ __global__ void v_scale_final_kernel(float* __restrict__ v_scale, int n) {
 }
 
 template <typename T, int D>
-static int launch_quant_v(const void* v, uint8_t* v8, float* v_scale, int BH, int N, cudaStream_t st) {
+static int launch_quant_v(const void* v, uint8_t* v8, float* v_scale, int BH, int H, int N, long long sb, long long sh,
+                          long long sn, cudaStream_t st) {
   const int N_pad = (N + 127) / 128 * 128;
   if (cudaMemsetAsync(v_scale, 0, (size_t)BH * D * sizeof(float), st) != cudaSuccess) return SPARGE_ERR_CUDA;
-  v_amax_kernel<T, D><<<dim3((N + kVRowsPerCta - 1) / kVRowsPerCta, BH), 256, 0, st>>>((const T*)v, (unsigned int*)v_scale, N);
-  v_quant_kernel<T, D><<<dim3((N_pad + kVRowsPerCta - 1) / kVRowsPerCta, BH), 256, 0, st>>>((const T*)v, v_scale, v8, N, N_pad);
+  v_amax_kernel<T, D><<<dim3((N + kVRowsPerCta - 1) / kVRowsPerCta, BH), 256, 0, st>>>((const T*)v, (unsigned int*)v_scale, N, H, sb, sh, sn);
+  v_quant_kernel<T, D><<<dim3((N_pad + kVRowsPerCta - 1) / kVRowsPerCta, BH), 256, 0, st>>>((const T*)v, v_scale, v8, N, N_pad, H, sb, sh, sn);
   v_scale_final_kernel<<<(BH * D + 255) / 256, 256, 0, st>>>(v_scale, BH * D);
   return launch_status();
 }
 
 }  // namespace sparge
 
-extern "C" int sparge_quant_v(const void* v, uint8_t* v8, float* v_scale, int B, int H, int N, int D, int dtype,
-                              sparge_stream_t stream) {
+extern "C" int sparge_quant_v_strided(const void* v, uint8_t* v8, float* v_scale, int B, int H, int N, int D, int dtype,
+                                      long long stride_b, long long stride_h, long long stride_n,
+                                      sparge_stream_t stream) {
   using namespace sparge;
   if (!v || !v8 || !v_scale) return SPARGE_ERR_NULL;
   if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (dtype != SPARGE_F16 && dtype != SPARGE_BF16))
     return SPARGE_ERR_INVALID_ARG;
   if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;
+  if (!strides_ok(v, stride_b, stride_h, stride_n)) return SPARGE_ERR_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const int BH = B * H;
-  if (dtype == SPARGE_F16)
-    return D == 64 ? launch_quant_v<__half, 64>(v, v8, v_scale, BH, N, st) : launch_quant_v<__half, 128>(v, v8, v_scale, BH, N, st);
-  return D == 64 ? launch_quant_v<__nv_bfloat16, 64>(v, v8, v_scale, BH, N, st)
-                 : launch_quant_v<__nv_bfloat16, 128>(v, v8, v_scale, BH, N, st);
+#define SPARGE_QV(T, DD) launch_quant_v<T, DD>(v, v8, v_scale, BH, H, N, stride_b, stride_h, stride_n, st)
+  if (dtype == SPARGE_F16) return D == 64 ? SPARGE_QV(__half, 64) : SPARGE_QV(__half, 128);
+  return D == 64 ? SPARGE_QV(__nv_bfloat16, 64) : SPARGE_QV(__nv_bfloat16, 128);
+#undef SPARGE_QV
+}
+
+extern "C" int sparge_quant_v(const void* v, uint8_t* v8, float* v_scale, int B, int H, int N, int D, int dtype,
+                              sparge_stream_t stream) {
+  return sparge_quant_v_strided(v, v8, v_scale, B, H, N, D, dtype, (long long)H * N * D, (long long)N * D, D, stream);
 }

@@ -36,6 +36,19 @@ def _need_cuda(*ts):
             raise RuntimeError("expected a contiguous tensor")
 
 
+def strided_ok(t: torch.Tensor) -> bool:
+    """True if a [B,H,N,D] view can be read in place: last dim contiguous, 16-byte aligned rows."""
+    return (t.dim() == 4 and t.stride(-1) == 1 and t.data_ptr() % 16 == 0
+            and all(st % 8 == 0 and st >= 0 for st in t.stride()[:3]) and t.stride(2) > 0)
+
+
+def _need_strided(t):
+    if not t.is_cuda:
+        raise RuntimeError("spargeattn_b200 runs on CUDA tensors only (no CPU path)")
+    if not strided_ok(t):
+        raise RuntimeError("expected a [B,H,N,D] view with contiguous last dimension, 16-byte aligned")
+
+
 def device_status_word(device) -> torch.Tensor:
     """One int32 per device that sparge_attn_fwd writes when a bounded in-kernel wait expires."""
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
@@ -54,18 +67,20 @@ def check_device_status(device=None) -> int:
 
 
 def k_mean(k: torch.Tensor) -> torch.Tensor:
-    _need_cuda(k)
+    _need_strided(k)
     B, H, N, D = k.shape
     km = torch.empty(B, H, 1, D, dtype=k.dtype, device=k.device)
     nbytes = _cabi.lib.sparge_k_mean_scratch_bytes(B, H, N, D)
     scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=k.device)
-    _cabi.check(_cabi.lib.sparge_k_mean(_ptr(k), _ptr(km), _ptr(scratch), B, H, N, D, _dt(k), _stream(k)), "sparge_k_mean")
+    _cabi.check(_cabi.lib.sparge_k_mean_strided(_ptr(k), _ptr(km), _ptr(scratch), B, H, N, D, _dt(k), k.stride(0),
+                                                k.stride(1), k.stride(2), _stream(k)), "sparge_k_mean")
     return km
 
 
 def pool_sim_quant(x: torch.Tensor, km: Optional[torch.Tensor], block: int, simthreshd1: Optional[torch.Tensor]):
     """Returns (pool, sim, x_int8, scale); pool and sim are None when simthreshd1 is None."""
-    _need_cuda(x, km, simthreshd1)
+    _need_strided(x)
+    _need_cuda(km, simthreshd1)
     B, H, N, D = x.shape
     nb = (N + block - 1) // block
     x8 = torch.empty(B, H, N, D, dtype=torch.int8, device=x.device)
@@ -74,8 +89,9 @@ def pool_sim_quant(x: torch.Tensor, km: Optional[torch.Tensor], block: int, simt
     if simthreshd1 is not None:
         pool = torch.empty(B, H, nb, D, dtype=x.dtype, device=x.device)
         sim = torch.empty(B, H, nb, dtype=torch.uint8, device=x.device)
-    _cabi.check(_cabi.lib.sparge_pool_quant(_ptr(x), _ptr(km), _ptr(simthreshd1), _ptr(pool), _ptr(sim), _ptr(x8),
-                                            _ptr(scale), B, H, N, D, block, _dt(x), _stream(x)), "sparge_pool_quant")
+    _cabi.check(_cabi.lib.sparge_pool_quant_strided(_ptr(x), _ptr(km), _ptr(simthreshd1), _ptr(pool), _ptr(sim),
+                                                    _ptr(x8), _ptr(scale), B, H, N, D, block, _dt(x), x.stride(0),
+                                                    x.stride(1), x.stride(2), _stream(x)), "sparge_pool_quant")
     return pool, sim, x8, scale
 
 
@@ -112,24 +128,27 @@ def mask_to_lut(block_map: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
 def quant_v(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """v [B,H,N,D] fp16/bf16 -> (v8 uint8 [B,H,N_pad,D] e4m3 bytes, v_scale [B,H,D])."""
-    _need_cuda(v)
+    _need_strided(v)
     B, H, N, D = v.shape
     npad = (N + 127) // 128 * 128
     v8 = torch.empty(B, H, npad, D, dtype=torch.uint8, device=v.device)
     vs = torch.empty(B, H, D, dtype=torch.float32, device=v.device)
-    _cabi.check(_cabi.lib.sparge_quant_v(_ptr(v), _ptr(v8), _ptr(vs), B, H, N, D, _dt(v), _stream(v)), "sparge_quant_v")
+    _cabi.check(_cabi.lib.sparge_quant_v_strided(_ptr(v), _ptr(v8), _ptr(vs), B, H, N, D, _dt(v), v.stride(0), v.stride(1),
+                                                 v.stride(2), _stream(v)), "sparge_quant_v")
     return v8, vs
 
 
 def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale, k_scale, v_scale, sm_scale: float,
              is_causal: bool, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    _need_cuda(q8, k8, v8, lut, valid, pvthreshd, q_scale, k_scale, v_scale, out)
+    _need_cuda(q8, k8, v8, lut, valid, pvthreshd, q_scale, k_scale, v_scale)
     B, H, N, D = q8.shape
     if out is None:
         out = torch.empty(B, H, N, D, dtype=out_dtype, device=q8.device)
+    _need_strided(out)
     status = device_status_word(q8.device)
-    _cabi.check(_cabi.lib.sparge_attn_fwd(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
-                                          _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale), _ptr(status),
-                                          B, H, N, D, _dt(out), int(bool(is_causal)), float(sm_scale), _stream(q8)),
-                "sparge_attn_fwd")
+    _cabi.check(_cabi.lib.sparge_attn_fwd_strided(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
+                                                  _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale),
+                                                  _ptr(status), B, H, N, D, _dt(out), int(bool(is_causal)),
+                                                  float(sm_scale), out.stride(0), out.stride(1), out.stride(2),
+                                                  _stream(q8)), "sparge_attn_fwd")
     return out

@@ -106,7 +106,18 @@ def test_nhd_layout_and_per_head_knobs():
                                            tensor_layout="NHD")
     _status_ok()
     assert o.shape == (B, N, H, D)
+    assert o.is_contiguous()                               # written in NHD directly, no permuted copy
     _check(o.transpose(1, 2), o_ref)
+    # reading the NHD tensors in place gives the same bytes as the HND-contiguous call
+    o_hnd = S.spas_sage2_attn_meansim_topk_cuda(q.cuda(), k.cuda(), v.cuda(), topk=topk, simthreshd1=0.3,
+                                                attention_sink=True)
+    assert torch.equal(o.transpose(1, 2), o_hnd)
+    # a view that cannot be read in place (odd storage offset) is copied, as the reference does
+    pad = torch.zeros(B, H, N, D + 1, dtype=q.dtype, device="cuda")
+    pad[..., 1:] = q.cuda()
+    o_odd = S.spas_sage2_attn_meansim_topk_cuda(pad[..., 1:], k.cuda(), v.cuda(), topk=topk, simthreshd1=0.3,
+                                                attention_sink=True)
+    assert torch.equal(o_odd, o_hnd)
 
 
 def test_pv_threshold_skips_blocks():
