@@ -312,7 +312,7 @@ def main():
         km = ops.k_mean(kc)
         pq, sq, q8, qs = ops.pool_sim_quant(qc, None, 128, thr)
         pk, sk, k8, ks = ops.pool_sim_quant(kc, km, 64, thr)
-        lut, valid, _ = ops.select_blocks(pq, pk, sq, sk, tk, None, causal, False)
+        lut, valid, _ = ops.select_blocks(pq, pk, sq, sk, tk, None, causal, False, best_first=pv is None)
         v8, vs = ops.quant_v(vc)
         nd = B * H * N * D
         nq, nk = (N + 127) // 128, (N + 63) // 64
@@ -323,7 +323,7 @@ def main():
         t = t_kernel(lambda: ops.pool_sim_quant(kc, km, 64, thr))
         kernels["pool_quant_k"] = {"ms": t, "GBps": 3 * nd / t / 1e6, "alg_bytes": 3 * nd}
         sel_bytes = B * H * (2 * (nq + nk) * D + nq * nk * 4)
-        t = t_kernel(lambda: ops.select_blocks(pq, pk, sq, sk, tk, None, causal, False))
+        t = t_kernel(lambda: ops.select_blocks(pq, pk, sq, sk, tk, None, causal, False, best_first=pv is None))
         kernels["select"] = {"ms": t, "GBps": sel_bytes / t / 1e6, "alg_bytes": sel_bytes}
         t = t_kernel(lambda: ops.quant_v(vc))
         kernels["quant_v"] = {"ms": t, "GBps": 3 * nd / t / 1e6, "alg_bytes": 3 * nd}

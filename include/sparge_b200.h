@@ -85,10 +85,14 @@ int sparge_pool_quant(const void* x, const void* km, const float* simthreshd1, v
  *   pq [B,H,nq,D], pk [B,H,nk,D] (16-bit), sim_q [B,H,nq], sim_k [B,H,nk] (uint8),
  *   topk [H] fp32 or NULL, cdfthreshd [H] fp32 or NULL (exactly one non-NULL),
  *   outputs: mask [B,H,nq,nk] uint8 (may be NULL), lut [B,H,nq,nk] int32 (first entry absolute,
- *   then gaps, zero tail), valid [B,H,nq] int32.  Ties are broken towards the lower block index. */
+ *   then gaps, zero tail), valid [B,H,nq] int32.  Ties are broken towards the lower block index.
+ *   lut_order: SPARGE_LUT_ASCENDING (0) is the reference encoding. SPARGE_LUT_BEST_FIRST (1) puts the live
+ *   block with the largest pooled probability first and keeps the others ascending (gaps may be negative;
+ *   sparge_attn_fwd simply accumulates them). It selects the same blocks; only the visiting order changes. */
+enum { SPARGE_LUT_ASCENDING = 0, SPARGE_LUT_BEST_FIRST = 1 };
 int sparge_select(const void* pq, const void* pk, const uint8_t* sim_q, const uint8_t* sim_k, const float* topk,
                   const float* cdfthreshd, uint8_t* mask, int32_t* lut, int32_t* valid, int B, int H, int nq,
-                  int nk, int D, int dtype, int is_causal, int attention_sink, sparge_stream_t stream);
+                  int nk, int D, int dtype, int is_causal, int attention_sink, int lut_order, sparge_stream_t stream);
 
 /* User block mask -> LUT.  Replaces block_map_lut_triton / triton_block_map_to_lut_kernel
  * (spas_sage_attn/utils.py:54-87).  mask [B,H,nq,nk] with elem_size in {1,2,4,8} bytes, any

@@ -26,7 +26,7 @@ SIGNATURES = {
     "sparge_k_mean": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "sparge_k_mean_static": (_i, [_p, _p, _i, _i, _i, _i, _i, _p]),
     "sparge_pool_quant": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
-    "sparge_select": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
+    "sparge_select": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "sparge_mask_to_lut": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _p]),
     "sparge_quant_v": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "sparge_k_mean_strided": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _ll, _ll, _ll, _p]),

@@ -92,8 +92,9 @@ def _empty_like_layout(q):
 
 def get_block_map_meansim_fuse_quant(q, k, km=None, is_causal=False, BLKQ=128, BLKK=64, simthreshd1=0.1,
                                      cdfthreshd=0.9, topk=None, is_sparse=True, return_lut=False,
-                                     attention_sink=False):
-    """spas_sage_attn/utils.py:371-421."""
+                                     attention_sink=False, best_first=False):
+    """spas_sage_attn/utils.py:371-421. `best_first` (not in the reference) reorders each LUT row so that the
+    block with the largest pooled probability is visited first; the selected set is unchanged."""
     assert (cdfthreshd is None and topk is not None) \
         or (cdfthreshd is not None and topk is None), "Only one of cdfthreshd and topk can be set."
     assert BLKQ == 128 and BLKK == 64, "this build fixes the sparsity block at 128 x 64"
@@ -106,7 +107,8 @@ def get_block_map_meansim_fuse_quant(q, k, km=None, is_causal=False, BLKQ=128, B
     pooled_q, sim_q, q_int8, q_scale = ops.pool_sim_quant(q, None, BLKQ, simthreshd1)
     pooled_k, sim_k, k_int8, k_scale = ops.pool_sim_quant(k, km, BLKK, simthreshd1)
     lut, valid_block_num, final_map = ops.select_blocks(pooled_q, pooled_k, sim_q, sim_k, topk, cdfthreshd, is_causal,
-                                                        attention_sink, want_mask=not return_lut)
+                                                        attention_sink, want_mask=not return_lut,
+                                                        best_first=best_first and return_lut)
     if not return_lut:
         return final_map.bool(), q_int8, q_scale, k_int8, k_scale
     return lut, valid_block_num, q_int8, q_scale, k_int8, k_scale
@@ -139,12 +141,14 @@ def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthre
     km = ops.k_mean(k) if smooth_k else None
     headdim = q.size(-1)
     assert headdim in [64, 128], "headdim should be in [64, 128]. For other headdim, you can use padding and specify the softmax scale."
+    pvthreshd = _pv_threshold_tensor(pvthreshd, q.size(-3), q.device)
+    # The PV-skip rule depends on the visiting order (it exempts the last two live blocks), so the
+    # best-first order is used only when the skip test is compiled out.
     lut, valid_block_num, q_int8, q_scale, k_int8, k_scale = get_block_map_meansim_fuse_quant(
         q, k, km, is_causal=is_causal, simthreshd1=simthreshd1, cdfthreshd=cdfthreshd, topk=topk, return_lut=True,
-        attention_sink=attention_sink, BLKQ=128, BLKK=64)
+        attention_sink=attention_sink, BLKQ=128, BLKK=64, best_first=pvthreshd is None)
     if scale is None:
         scale = 1.0 / (headdim ** 0.5)
-    pvthreshd = _pv_threshold_tensor(pvthreshd, q.size(-3), q.device)
     v_fp8, v_scale = ops.quant_v(v)
     o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale,
                      kernel_causal, q.dtype, out=_empty_like_layout(q))

@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kSelRowsPerCta * 32)
 select_kernel(const T* __restrict__ pq, const T* __restrict__ pk, const uint8_t* __restrict__ sim_q,
               const uint8_t* __restrict__ sim_k, const float* __restrict__ topk, const float* __restrict__ cdfthr,
               uint8_t* __restrict__ mask, int32_t* __restrict__ lut, int32_t* __restrict__ valid, int H, int nq, int nk,
-              int is_causal, int sink, int rows_per_cta) {
+              int is_causal, int sink, int rows_per_cta, int best_first) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int qi = blockIdx.x * rows_per_cta + warp, bh = blockIdx.y, h = bh % H;
@@ -258,9 +258,35 @@ select_kernel(const T* __restrict__ pq, const T* __restrict__ pk, const uint8_t*
   }
   __syncwarp();
   int32_t* lrow = lut + ((size_t)bh * nq + qi) * nk;
+  // Visiting order. Reference order: ascending block index. Best-first: the live block with the largest
+  // pooled probability (lowest index on ties) is moved to the front and the rest stay ascending; the
+  // deltas may then be negative. Attention is order-independent, but starting at the block that most
+  // likely holds the row maxima makes later rescales of the running output rare.
+  int rbest = 0;
+  if (best_first && live_seen > 1) {
+    uint32_t bk = 0;
+    int bpos = 0x7fffffff;
+    for (int r = lane; r < live_seen; r += 32) {
+      const uint32_t key = s_key[s_idx[r]];
+      if (key > bk || (key == bk && r < bpos)) { bk = key; bpos = r; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const uint32_t ok_ = __shfl_xor_sync(0xffffffffu, bk, o);
+      const int op = __shfl_xor_sync(0xffffffffu, bpos, o);
+      if (ok_ > bk || (ok_ == bk && op < bpos)) { bk = ok_; bpos = op; }
+    }
+    rbest = (bpos == 0x7fffffff) ? 0 : bpos;
+  }
+  const int jbest = (live_seen > 0) ? s_idx[rbest] : 0;
   for (int r = lane; r < nk; r += 32) {
     int vv = 0;
-    if (r < live_seen) vv = s_idx[r] - (r > 0 ? s_idx[r - 1] : 0);
+    if (r < live_seen) {
+      // element at visiting position r: jbest first, then the ascending list without it
+      const int cur = (r == 0) ? jbest : s_idx[r <= rbest ? r - 1 : r];
+      const int prev = (r == 0) ? 0 : ((r == 1) ? jbest : s_idx[(r - 1) <= rbest ? r - 2 : r - 1]);
+      vv = cur - prev;
+    }
     lrow[r] = vv;
   }
   if (lane == 0) valid[(size_t)bh * nq + qi] = live_seen;
@@ -301,7 +327,7 @@ __global__ void __launch_bounds__(kSelThreads) mask_to_lut_kernel(const uint8_t*
 template <typename T, int D>
 static int launch_select(const void* pq, const void* pk, const uint8_t* sim_q, const uint8_t* sim_k, const float* topk,
                          const float* cdf, uint8_t* mask, int32_t* lut, int32_t* valid, int BH, int H, int nq, int nk,
-                         int causal, int sink, cudaStream_t st) {
+                         int causal, int sink, int best_first, cudaStream_t st) {
   const size_t row_bytes = select_row_bytes(nk, D);
   const size_t tile_bytes = 32 * (D * sizeof(T) + 16);
   const size_t budget = 200 * 1024 - tile_bytes;
@@ -314,7 +340,7 @@ static int launch_select(const void* pq, const void* pk, const uint8_t* sim_q, c
       return SPARGE_ERR_CUDA;
   }
   kern<<<dim3((nq + rows - 1) / rows, BH), kSelRowsPerCta * 32, smem, st>>>(
-      (const T*)pq, (const T*)pk, sim_q, sim_k, topk, cdf, mask, lut, valid, H, nq, nk, causal, sink, rows);
+      (const T*)pq, (const T*)pk, sim_q, sim_k, topk, cdf, mask, lut, valid, H, nq, nk, causal, sink, rows, best_first);
   return launch_status();
 }
 
@@ -323,7 +349,7 @@ static int launch_select(const void* pq, const void* pk, const uint8_t* sim_q, c
 extern "C" int sparge_select(const void* pq, const void* pk, const uint8_t* sim_q, const uint8_t* sim_k,
                              const float* topk, const float* cdfthreshd, uint8_t* mask, int32_t* lut, int32_t* valid,
                              int B, int H, int nq, int nk, int D, int dtype, int is_causal, int attention_sink,
-                             sparge_stream_t stream) {
+                             int lut_order, sparge_stream_t stream) {
   using namespace sparge;
   if (!pq || !pk || !sim_q || !sim_k || !lut || !valid) return SPARGE_ERR_NULL;
   if ((topk == nullptr) == (cdfthreshd == nullptr)) return SPARGE_ERR_INVALID_ARG;
@@ -333,7 +359,7 @@ extern "C" int sparge_select(const void* pq, const void* pk, const uint8_t* sim_
   cudaStream_t st = (cudaStream_t)stream;
   const int BH = B * H;
 #define SPARGE_SEL(T, DD) \
-  launch_select<T, DD>(pq, pk, sim_q, sim_k, topk, cdfthreshd, mask, lut, valid, BH, H, nq, nk, is_causal, attention_sink, st)
+  launch_select<T, DD>(pq, pk, sim_q, sim_k, topk, cdfthreshd, mask, lut, valid, BH, H, nq, nk, is_causal, attention_sink, lut_order != 0, st)
   if (dtype == SPARGE_F16) return D == 64 ? SPARGE_SEL(__half, 64) : SPARGE_SEL(__half, 128);
   return D == 64 ? SPARGE_SEL(__nv_bfloat16, 64) : SPARGE_SEL(__nv_bfloat16, 128);
 #undef SPARGE_SEL

@@ -96,8 +96,8 @@ def pool_sim_quant(x: torch.Tensor, km: Optional[torch.Tensor], block: int, simt
 
 
 def select_blocks(pq, pk, sim_q, sim_k, topk: Optional[torch.Tensor], cdfthreshd: Optional[torch.Tensor],
-                  is_causal: bool, attention_sink: bool, want_mask: bool = False):
-    """Returns (lut, valid, mask-or-None)."""
+                  is_causal: bool, attention_sink: bool, want_mask: bool = False, best_first: bool = False):
+    """Returns (lut, valid, mask-or-None). best_first=False gives the reference's ascending LUT."""
     _need_cuda(pq, pk, sim_q, sim_k, topk, cdfthreshd)
     B, H, nq, D = pq.shape
     nk = pk.shape[2]
@@ -106,7 +106,8 @@ def select_blocks(pq, pk, sim_q, sim_k, topk: Optional[torch.Tensor], cdfthreshd
     mask = torch.empty(B, H, nq, nk, dtype=torch.uint8, device=pq.device) if want_mask else None
     _cabi.check(_cabi.lib.sparge_select(_ptr(pq), _ptr(pk), _ptr(sim_q), _ptr(sim_k), _ptr(topk), _ptr(cdfthreshd),
                                         _ptr(mask), _ptr(lut), _ptr(valid), B, H, nq, nk, D, _dt(pq),
-                                        int(bool(is_causal)), int(bool(attention_sink)), _stream(pq)), "sparge_select")
+                                        int(bool(is_causal)), int(bool(attention_sink)), int(bool(best_first)),
+                                        _stream(pq)), "sparge_select")
     return lut, valid, mask
 
 

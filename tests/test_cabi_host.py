@@ -38,8 +38,8 @@ def test_null_and_bad_arguments_return_status_codes():
     assert L.sparge_pool_quant(one, None, None, None, None, None, one, 1, 1, 128, 64, 128, 0, None) == _cabi.ERR_NULL
     assert L.sparge_pool_quant(one, None, None, None, None, one, one, 1, 1, 128, 64, 32, 0, None) == _cabi.ERR_INVALID_ARG
     assert L.sparge_pool_quant(one, None, one, None, None, one, one, 1, 1, 128, 64, 64, 0, None) == _cabi.ERR_NULL
-    assert L.sparge_select(one, one, one, one, one, one, None, one, one, 1, 1, 1, 2, 64, 0, 0, 0, None) == _cabi.ERR_INVALID_ARG
-    assert L.sparge_select(one, one, one, one, None, None, None, one, one, 1, 1, 1, 2, 64, 0, 0, 0, None) == _cabi.ERR_INVALID_ARG
+    assert L.sparge_select(one, one, one, one, one, one, None, one, one, 1, 1, 1, 2, 64, 0, 0, 0, 0, None) == _cabi.ERR_INVALID_ARG
+    assert L.sparge_select(one, one, one, one, None, None, None, one, one, 1, 1, 1, 2, 64, 0, 0, 0, 0, None) == _cabi.ERR_INVALID_ARG
     assert L.sparge_mask_to_lut(one, 3, one, one, 1, 1, 1, 2, None) == _cabi.ERR_INVALID_ARG
     assert L.sparge_quant_v(one, one, None, 1, 1, 128, 64, 0, None) == _cabi.ERR_NULL
     assert L.sparge_quant_v(one, one, one, 70000, 1, 128, 64, 0, None) == _cabi.ERR_TOO_LARGE

@@ -28,9 +28,11 @@ def test_wan_shape_all_blocks_live_equals_sdpa():
     ref = torch.nn.functional.scaled_dot_product_attention(q, k, v)
     m = _metric(o, ref)
     assert m["Cossim"] >= 0.995 and m["L1"] <= 0.06, m     # INT8 QK / FP8 PV quantisation error vs bf16 flash attention
-    # top-k = 1 selects every block: the predictor path must give the same bytes as the explicit all-ones mask
+    # top-k = 1 selects every block: the predictor path computes the same attention as the explicit all-ones
+    # mask, visiting the blocks in another order (best pooled block first), so equal up to rounding
     o2 = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=1.0)
-    assert torch.equal(o, o2)
+    m2 = _metric(o2, o)
+    assert m2["Cossim"] >= 0.9999 and m2["L1"] <= 5e-3, m2
 
 
 def test_llama_shape_causal_topk1_equals_causal_sdpa():

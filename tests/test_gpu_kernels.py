@@ -138,6 +138,30 @@ def test_select_cdf_mode_bit_exact(shape, dtype, causal, cdf):
     assert torch.equal(valid.cpu(), pr["valid"]) and torch.equal(lut.cpu(), pr["lut"])
 
 
+def test_select_best_first_order_is_a_permutation_of_the_reference_lut():
+    ops = _ops()
+    B, H, N, D = 2, 2, 3000, 64
+    q, k = _rand_qk(B, H, N, D, torch.bfloat16, 9)
+    pr = O.predictor(q, k, O.k_mean(k), False, torch.full((H,), 0.2), None, torch.full((H,), 0.4), False)
+    args = (pr["pq"].cuda(), pr["pk"].cuda(), pr["sim_q"].to(torch.uint8).cuda(), pr["sim_k"].to(torch.uint8).cuda(),
+            torch.full((H,), 0.4).cuda(), None, False, False)
+    lut_a, valid_a, _ = ops.select_blocks(*args, best_first=False)
+    lut_b, valid_b, _ = ops.select_blocks(*args, best_first=True)
+    assert torch.equal(valid_a, valid_b) and torch.equal(lut_a.cpu(), pr["lut"])
+    idx_a, idx_b = torch.cumsum(lut_a.cpu(), -1), torch.cumsum(lut_b.cpu(), -1)
+    p = pr["p"].float()
+    for b in range(B):
+        for h in range(H):
+            for r in range(idx_a.shape[2]):
+                n = int(valid_a[b, h, r])
+                a, bb = idx_a[b, h, r, :n], idx_b[b, h, r, :n]
+                assert torch.equal(torch.sort(bb).values, a)                      # same set of blocks
+                assert torch.equal(bb[1:], a[a != bb[0]])                          # the rest stays ascending
+                best = p[b, h, r, a]
+                assert bb[0] == a[torch.argmax(best)]                             # highest probability, lowest index on ties
+                assert (lut_b[b, h, r, n:] == 0).all()
+
+
 def test_select_ties_go_to_lower_index():
     """Identical pooled keys give identical probabilities: the stable order must keep the lowest indices."""
     ops = _ops()
