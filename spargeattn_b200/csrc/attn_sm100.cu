@@ -271,17 +271,18 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         rmax = (klim > 0) ? __int2float_rn(mx) * c : kMaskValue;
       }
       const float m_new = fmaxf(m, rmax);
-      bool skip = false;
-      if (PV_SKIP && n < cnt - 2) {   // the last two live blocks are never skipped
+      // PV-skip test (qk_int_sv_f8_cuda_sm89.cuh:317-353): the block is skipped when, over all 128 rows,
+      // max(row maximum - running maximum) + threshold <= 0. The four warps publish their partial maxima
+      // now and read the result only after the exponentials, so the reduction latency is hidden; a block
+      // that turns out to be skipped has wasted its exponentials (rare) but leaves no trace: its row sums
+      // are dropped and the MMA warp does not issue its PV product.
+      const bool skip_candidate = PV_SKIP && n < cnt - 2;   // the last two live blocks are never skipped
+      if (skip_candidate) {
         const float wmax = warp_max(rmax - m);
         if (lane == 0) {
           s_delta[b][warp] = wmax;
           mbar_arrive(&bar_delta[b]);
         }
-        ok = mbar_wait(&bar_delta[b], (n >> 1) & 1);
-        if (!ok) break;
-        const float dcta = fmaxf(fmaxf(s_delta[b][0], s_delta[b][1]), fmaxf(s_delta[b][2], s_delta[b][3]));
-        skip = (dcta + thr <= 0.f);
       }
       // Rescaling of the running output is deferred until after the exponentials: by then PV(n-1) has
       // normally retired, so the wait below does not stall. The wait itself is unconditional: a parity
@@ -314,15 +315,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       };
       d *= alpha;
       m = m_new;
-      if (skip) {
-        ok = settle_output();
-        if (!ok) break;
-        if (tid == 0) s_skip[b] = 1;
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_p_ready[b]);
-        continue;
-      }
       uint32_t pr[16];
       float sum;
       if (!masked_block) {
@@ -366,12 +358,21 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
           pr[k >> 2] = cvt_e4m3x4(p0, p1, p2, p3);
         }
       }
-      d += sum;
+      bool skip = false;
+      if (skip_candidate) {
+        ok = mbar_wait(&bar_delta[b], (n >> 1) & 1);
+        if (!ok) break;
+        const float dcta = fmaxf(fmaxf(s_delta[b][0], s_delta[b][1]), fmaxf(s_delta[b][2], s_delta[b][3]));
+        skip = (dcta + thr <= 0.f);
+      }
+      if (!skip) d += sum;
       ok = settle_output();
       if (!ok) break;
-      tmem_st16(tS, pr);
-      tmem_wait_st();
-      if (PV_SKIP && tid == 0) s_skip[b] = 0;
+      if (!skip) {
+        tmem_st16(tS, pr);
+        tmem_wait_st();
+      }
+      if (PV_SKIP && tid == 0) s_skip[b] = skip ? 1 : 0;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_p_ready[b]);
