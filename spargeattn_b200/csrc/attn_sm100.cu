@@ -27,6 +27,7 @@ constexpr float kFp8Offset = 8.807f;     // csrc/qattn/attn_utils.cuh:28-30: 2^8
 constexpr float kMaskValue = -5000000.0f;  // csrc/qattn/attn_utils.cuh:348-352
 constexpr uint32_t kMagicBits = 0x4B400000u;   // bit pattern of 12582912.0f = 1.5 * 2^23
 constexpr float kMagic = 12582912.0f;
+constexpr float kFastScaleLimit = 0.0078125f;  // 2^-7: bounds the fast path's per-block weight error by 0.41 %
 
 
 template <int D>
@@ -317,9 +318,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       m = m_new;
       uint32_t pr[16];
       float sum;
-      if (!masked_block) {
+      if (!masked_block && c < kFastScaleLimit) {
         // int32 -> fp32 by adding the bit pattern of 1.5 * 2^23 (exact for |S| < 2^22; here |S| <= 127^2 * 128);
         // the 2^23 bias is taken out again inside the FMA constant. Packed f32x2 FMA / ADD halve the issue slots.
+        // That constant is rounded at the magnitude of 1.5 * 2^23 * c, so the exponents of this block are off
+        // by a common amount of at most 0.75 * c: blocks whose scale is not small take the exact path below.
         const float off = fmaf(-kMagic, c, kFp8Offset - m);
         const float2 c2 = make_float2(c, c), o2 = make_float2(off, off);
         float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);

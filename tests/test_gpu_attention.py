@@ -174,3 +174,43 @@ def test_host_front_end_matches_device_call():
         torch.cuda.synchronize()
         assert torch.equal(out, ref.cpu())
     _status_ok()
+
+
+@pytest.mark.parametrize("N", [128, 129, 191, 257])
+def test_tiny_and_ragged_lengths(N):
+    import spargeattn_b200 as S
+    q, k, v = _inputs(1, 2, N, 64, torch.bfloat16, 19)
+    o_ref = O.spas_sage2_attn_meansim_topk(q, k, v, topk=0.5)
+    o = S.spas_sage2_attn_meansim_topk_cuda(q.cuda(), k.cuda(), v.cuda(), topk=0.5)
+    _status_ok()
+    _check(o, o_ref)
+
+
+def test_degenerate_inputs_do_not_stall_or_poison():
+    """All-zero tensors, huge magnitudes and a constant K: finite (or zero) outputs, no bounded wait expires."""
+    import spargeattn_b200 as S
+    B, H, N, D = 1, 2, 640, 128
+    z = torch.zeros(B, H, N, D, dtype=torch.bfloat16, device="cuda")
+    q, k, v = (t.cuda() for t in _inputs(B, H, N, D, torch.bfloat16, 20))
+    o = S.spas_sage2_attn_meansim_topk_cuda(z, z, z, topk=0.5)
+    assert torch.count_nonzero(o) == 0
+    o = S.spas_sage2_attn_meansim_topk_cuda(q, k, z, topk=0.5)            # all-zero V -> zeros, not NaN
+    assert torch.count_nonzero(o) == 0
+    S.spas_sage2_attn_meansim_topk_cuda(q * 1e4, k * 1e4, v * 1e3, topk=0.5)   # scores beyond fp32 resolution: only no stall
+    kc = torch.ones_like(k)                                                # constant K: smoothed K is all zero
+    o = S.spas_sage2_attn_meansim_topk_cuda(q, kc, v, topk=0.5)
+    assert torch.isfinite(o.float()).all()
+    _status_ok()
+
+
+@pytest.mark.parametrize("gain", [4.0, 20.0])
+def test_large_score_scale_takes_the_exact_exponent_path(gain):
+    """Per-block scales above 2^-7 leave the biased-FMA exponent path (its constant would be rounded too
+    coarsely) for the exact int->float one; the result must stay within the usual tolerance."""
+    import spargeattn_b200 as S
+    q, k, v = _inputs(1, 2, 1024, 128, torch.bfloat16, 21)
+    q, k = q * gain, k * gain
+    o_ref = O.spas_sage2_attn_meansim_topk(q, k, v, topk=0.5)
+    o = S.spas_sage2_attn_meansim_topk_cuda(q.cuda(), k.cuda(), v.cuda(), topk=0.5)
+    _status_ok()
+    _check(o, o_ref)
