@@ -145,6 +145,18 @@ int sparge_attn_fwd_strided(const int8_t* q_int8, const int8_t* k_int8, const ui
                             int is_causal, float sm_scale, long long o_stride_b, long long o_stride_h,
                             long long o_stride_n, sparge_stream_t stream);
 
+/* sparge_attn_fwd_strided plus the reference's return_pv_count diagnostic (csrc/qattn/qk_int_sv_f8_cuda_sm89.cu:526-529,
+ * kernel qk_int_sv_f8_cuda_sm89.cuh:91,355-358,650-656): pv_count is int32 [B, H, ceil(N/128) * 4], one entry per
+ * 32-row group of a query block, = the number of live blocks whose P.V product was computed (valid[b,h,q] minus the
+ * blocks dropped by the pvthreshd test; the test is per 128-row block here, so the four entries are equal).
+ * pv_count may be NULL (then identical to sparge_attn_fwd_strided). The caller allocates it; the reference allocates
+ * it inside the op. */
+int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o, const int32_t* lut,
+                             const int32_t* valid, const float* pvthreshd, const float* q_scale, const float* k_scale,
+                             const float* v_scale, int32_t* dev_status, int B, int H, int N, int D, int out_dtype,
+                             int is_causal, float sm_scale, long long o_stride_b, long long o_stride_h,
+                             long long o_stride_n, int32_t* pv_count, sparge_stream_t stream);
+
 /* Failure-detection self test: launches one warp that waits on a barrier nobody signals, bounded by
  * slices x slice_ns nanoseconds (at most 0.1 s in total), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into
  * *dev_status when the bounded wait gives up -- the same code path that sparge_attn_fwd takes if a

@@ -33,6 +33,7 @@ SIGNATURES = {
     "sparge_pool_quant_strided": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _p]),
     "sparge_quant_v_strided": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _ll, _ll, _ll, _p]),
     "sparge_attn_fwd_strided": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _ll, _ll, _ll, _p]),
+    "sparge_attn_fwd_pv_count": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _ll, _ll, _ll, _p, _p]),
     "sparge_selftest_wait_expiry": (_i, [_p, ctypes.c_uint, ctypes.c_uint, _p]),
     "sparge_attn_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p]),
 }

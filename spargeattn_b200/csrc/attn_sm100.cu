@@ -63,7 +63,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
             const __grid_constant__ CUtensorMap tmap_v, OutT* __restrict__ o, const int32_t* __restrict__ lut,
             const int32_t* __restrict__ valid, const float* __restrict__ pvthr, const float* __restrict__ q_scale,
             const float* __restrict__ k_scale, const float* __restrict__ v_scale, int32_t* dev_status, int N, int H,
-            int nq, int nk, float sm_scale_log2, int one, long long osb, long long osh, long long osn) {
+            int nq, int nk, float sm_scale_log2, int one, long long osb, long long osh, long long osn,
+            int32_t* __restrict__ pv_count) {
   using Shape = AttnShape<D>;
   constexpr int STAGES = Shape::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -91,6 +92,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     OutT* obase = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qi * 128 * osn;
     for (int i = tid; i < rows * kChunks; i += 192)
       reinterpret_cast<uint4*>(obase + (size_t)(i / kChunks) * osn)[i % kChunks] = make_uint4(0, 0, 0, 0);
+    if (pv_count && tid < 4) pv_count[row_id * 4 + tid] = 0;
     return;
   }
 
@@ -229,6 +231,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     float ks_nxt = ksc[j_nxt];
     int delta_nn = (cnt > 2) ? lrow[2] : 0;
     bool ok = true;
+    int npv = 0;   // PV products issued for this query block (all of them unless the skip test fires)
     for (int n = 0; n < cnt; n++) {
       const int j = j_cur;
       const float c = qs * ks_cur;
@@ -368,7 +371,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         const float dcta = fmaxf(fmaxf(s_delta[b][0], s_delta[b][1]), fmaxf(s_delta[b][2], s_delta[b][3]));
         skip = (dcta + thr <= 0.f);
       }
-      if (!skip) d += sum;
+      if (!skip) {
+        d += sum;
+        npv++;
+      }
       ok = settle_output();
       if (!ok) break;
       if (!skip) {
@@ -383,6 +389,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     if (ok) ok = mbar_wait(&bar_o_done, (cnt - 1) & 1);
     if (ok) {
       tc_fence_after();
+      // One count per 32-row group, the layout of the reference's PV_Count (qk_int_sv_f8_cuda_sm89.cuh:650-656);
+      // the skip decision is taken per block, so the four entries of a block are equal.
+      if (pv_count && lane == 0) pv_count[row_id * 4 + warp] = npv;
       const float inv = rcp_approx(d);
       const float* vs = v_scale + (size_t)bh * D;
       OutT* orow = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qrow * osn;
@@ -447,7 +456,7 @@ template <int D, bool CAUSAL, bool PV_SKIP, typename OutT>
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, const int32_t* lut,
                        const int32_t* valid, const float* pvthr, const float* qs, const float* ks, const float* vs,
                        int32_t* status, int BH, int H, int N, float sm_scale_log2, long long osb, long long osh,
-                       long long osn, cudaStream_t st) {
+                       long long osn, int32_t* pv_count, cudaStream_t st) {
   auto kern = attn_kernel<D, CAUSAL, PV_SKIP, OutT>;
   constexpr int smem = AttnShape<D>::kSmemBytes;
   // function attributes are per device: set on every call (cheap) rather than caching
@@ -455,7 +464,7 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   const int nq = (N + 127) / 128, nk = (N + 63) / 64;
   kern<<<dim3(nq, BH), 192, smem, st>>>(tq, tk, tv, (OutT*)o, lut, valid, pvthr, qs, ks, vs, status, N, H, nq, nk,
-                                        sm_scale_log2, 1, osb, osh, osn);
+                                        sm_scale_log2, 1, osb, osh, osn, pv_count);
   return launch_status();
 }
 
@@ -482,12 +491,12 @@ extern "C" int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int sli
   return sparge::launch_status();
 }
 
-extern "C" int sparge_attn_fwd_strided(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
-                                       const int32_t* lut, const int32_t* valid, const float* pvthreshd,
-                                       const float* q_scale, const float* k_scale, const float* v_scale,
-                                       int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
-                                       float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
-                                       sparge_stream_t stream) {
+extern "C" int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
+                                        const int32_t* lut, const int32_t* valid, const float* pvthreshd,
+                                        const float* q_scale, const float* k_scale, const float* v_scale,
+                                        int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
+                                        float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
+                                        int32_t* pv_count, sparge_stream_t stream) {
   using namespace sparge;
   if (!q_int8 || !k_int8 || !v8 || !o || !lut || !valid || !q_scale || !k_scale || !v_scale) return SPARGE_ERR_NULL;
   if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (out_dtype != SPARGE_F16 && out_dtype != SPARGE_BF16))
@@ -504,7 +513,7 @@ extern "C" int sparge_attn_fwd_strided(const int8_t* q_int8, const int8_t* k_int
   const float sl2 = sm_scale * kLog2e;
   const bool causal = is_causal != 0, skip = pvthreshd != nullptr, bf = out_dtype == SPARGE_BF16;
 #define SPARGE_ATTN(DD, C, S, T) \
-  launch_attn<DD, C, S, T>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, BH, H, N, sl2, o_stride_b, o_stride_h, o_stride_n, st)
+  launch_attn<DD, C, S, T>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, BH, H, N, sl2, o_stride_b, o_stride_h, o_stride_n, pv_count, st)
 #define SPARGE_ATTN_T(DD, C, S) (bf ? SPARGE_ATTN(DD, C, S, __nv_bfloat16) : SPARGE_ATTN(DD, C, S, __half))
 #define SPARGE_ATTN_S(DD, C) (skip ? SPARGE_ATTN_T(DD, C, true) : SPARGE_ATTN_T(DD, C, false))
 #define SPARGE_ATTN_C(DD) (causal ? SPARGE_ATTN_S(DD, true) : SPARGE_ATTN_S(DD, false))
@@ -513,6 +522,16 @@ extern "C" int sparge_attn_fwd_strided(const int8_t* q_int8, const int8_t* k_int
 #undef SPARGE_ATTN_S
 #undef SPARGE_ATTN_T
 #undef SPARGE_ATTN
+}
+
+extern "C" int sparge_attn_fwd_strided(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
+                                       const int32_t* lut, const int32_t* valid, const float* pvthreshd,
+                                       const float* q_scale, const float* k_scale, const float* v_scale,
+                                       int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
+                                       float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
+                                       sparge_stream_t stream) {
+  return sparge_attn_fwd_pv_count(q_int8, k_int8, v8, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, B, H,
+                                  N, D, out_dtype, is_causal, sm_scale, o_stride_b, o_stride_h, o_stride_n, nullptr, stream);
 }
 
 extern "C" int sparge_attn_fwd(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,

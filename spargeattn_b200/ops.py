@@ -140,16 +140,20 @@ def quant_v(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
 
 def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale, k_scale, v_scale, sm_scale: float,
-             is_causal: bool, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+             is_causal: bool, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
+             return_pv_count: bool = False):
+    """Block-sparse attention. With `return_pv_count` also returns int32 [B, H, ceil(N/128)*4]: per 32-row group the
+    number of P.V products computed (the `return_pv_count` diagnostic of csrc/qattn/qk_int_sv_f8_cuda_sm89.cu:526-584)."""
     _need_cuda(q8, k8, v8, lut, valid, pvthreshd, q_scale, k_scale, v_scale)
     B, H, N, D = q8.shape
     if out is None:
         out = torch.empty(B, H, N, D, dtype=out_dtype, device=q8.device)
     _need_strided(out)
     status = device_status_word(q8.device)
-    _cabi.check(_cabi.lib.sparge_attn_fwd_strided(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
-                                                  _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale),
-                                                  _ptr(status), B, H, N, D, _dt(out), int(bool(is_causal)),
-                                                  float(sm_scale), out.stride(0), out.stride(1), out.stride(2),
-                                                  _stream(q8)), "sparge_attn_fwd")
-    return out
+    pv_count = torch.empty(B, H, (N + 127) // 128 * 4, dtype=torch.int32, device=q8.device) if return_pv_count else None
+    _cabi.check(_cabi.lib.sparge_attn_fwd_pv_count(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
+                                                   _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale),
+                                                   _ptr(status), B, H, N, D, _dt(out), int(bool(is_causal)),
+                                                   float(sm_scale), out.stride(0), out.stride(1), out.stride(2),
+                                                   _ptr(pv_count), _stream(q8)), "sparge_attn_fwd")
+    return (out, pv_count) if return_pv_count else out

@@ -214,3 +214,32 @@ def test_large_score_scale_takes_the_exact_exponent_path(gain):
     o = S.spas_sage2_attn_meansim_topk_cuda(q.cuda(), k.cuda(), v.cuda(), topk=0.5)
     _status_ok()
     _check(o, o_ref)
+
+
+def test_return_pv_count_matches_oracle_skip_count():
+    """`return_pv_count` diagnostic: entries = live blocks minus the blocks dropped by the pvthreshd test."""
+    from spargeattn_b200 import ops
+    B, H, N, D = 1, 2, 2048, 64
+    q, k, v = _inputs(B, H, N, D, torch.bfloat16, 14)
+    q = q * 3
+    _, parts = O.spas_sage2_attn_meansim_topk(q, k, v, topk=0.6, pvthreshd=4.0, return_parts=True)
+    pv = O.hyperparameter_check(4.0, H)
+    _, skipped = O.attention_blockwise(parts["q_int8"], parts["q_scale"], parts["k_int8"], parts["k_scale"],
+                                       parts["v8"], parts["v_scale"], parts["map"], D ** -0.5, pv)
+    lut, valid = O.block_map_to_lut(parts["map"])
+    dev = lambda t: t.cuda().contiguous()
+    v8_bits = O.e4m3_bits(parts["v8"])
+    args = (dev(parts["q_int8"]), dev(parts["k_int8"]), dev(v8_bits), dev(lut.int()), dev(valid.int()))
+    scales = (dev(parts["q_scale"]), dev(parts["k_scale"]), dev(parts["v_scale"]))
+    # without the test every live block is computed
+    _, cnt = ops.attn_fwd(*args, None, *scales, D ** -0.5, False, torch.bfloat16, return_pv_count=True)
+    cnt = cnt.cpu().view(B, H, -1, 4)
+    assert (cnt == valid.int().unsqueeze(-1)).all()
+    # with it: four equal entries per block, never above the live count, total = oracle's (decisions at the
+    # threshold may differ by rounding of the running maximum: allow 1 %)
+    _, cnt = ops.attn_fwd(*args, dev(pv), *scales, D ** -0.5, False, torch.bfloat16, return_pv_count=True)
+    _status_ok()
+    cnt = cnt.cpu().view(B, H, -1, 4)
+    assert (cnt == cnt[..., :1]).all() and (cnt[..., 0] <= valid.int()).all() and (cnt[..., 0] >= valid.int().clamp(max=2)).all()
+    gpu_skipped = int(valid.sum()) - int(cnt[..., 0].sum())
+    assert skipped > 0 and abs(gpu_skipped - skipped) <= max(1, skipped // 100), (gpu_skipped, skipped)
