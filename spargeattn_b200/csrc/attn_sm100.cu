@@ -260,13 +260,17 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       }
       float rmax;
       if (!masked_block) {
-        int m0 = (int)sr[0], m1 = (int)sr[32];
+        int m0 = (int)sr[0], m1 = (int)sr[16], m2 = (int)sr[32], m3 = (int)sr[48];   // four chains: short latency
 #pragma unroll
-        for (int k = 1; k < 31; k += 2) {
+        for (int k = 1; k < 15; k += 2) {
           m0 = __vimax3_s32(m0, (int)sr[k], (int)sr[k + 1]);
-          m1 = __vimax3_s32(m1, (int)sr[32 + k], (int)sr[32 + k + 1]);
+          m1 = __vimax3_s32(m1, (int)sr[16 + k], (int)sr[16 + k + 1]);
+          m2 = __vimax3_s32(m2, (int)sr[32 + k], (int)sr[32 + k + 1]);
+          m3 = __vimax3_s32(m3, (int)sr[48 + k], (int)sr[48 + k + 1]);
         }
-        const int mx = __vimax3_s32(max(m0, m1), (int)sr[31], (int)sr[63]);
+        m0 = __vimax3_s32(m0, m1, (int)sr[15]);
+        m2 = __vimax3_s32(m2, m3, (int)sr[31]);
+        const int mx = max(__vimax3_s32(m0, m2, (int)sr[47]), (int)sr[63]);
         rmax = (__int_as_float(mx + (int)kMagicBits) - kMagic) * c;   // c > 0: max commutes with the scaling
       } else {
         int mx = INT_MIN;
@@ -344,6 +348,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
           s0 = __fadd2_rn(s0, a);
           s1 = __fadd2_rn(s1, bb);
           pr[k >> 2] = cvt_e4m3x4(a.x, a.y, bb.x, bb.y);
+          // P goes to TMEM four words at a time, as soon as they exist, instead of being parked in 16
+          // registers until the end of the block.
+          if ((k & 12) == 12) tmem_st4(tS + (k >> 2) - 3, pr + (k >> 2) - 3);
         }
         s0 = __fadd2_rn(s0, s1);
         sum = s0.x + s0.y;
@@ -363,6 +370,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
           sum += (p0 + p1) + (p2 + p3);
           pr[k >> 2] = cvt_e4m3x4(p0, p1, p2, p3);
         }
+        tmem_st16(tS, pr);
       }
       bool skip = false;
       if (skip_candidate) {
@@ -377,10 +385,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       }
       ok = settle_output();
       if (!ok) break;
-      if (!skip) {
-        tmem_st16(tS, pr);
-        tmem_wait_st();
-      }
+      tmem_wait_st();   // P of a skipped block is stored too; its PV product is simply never issued
       if (PV_SKIP && tid == 0) s_skip[b] = skip ? 1 : 0;
       tc_fence_before();
       __syncwarp();
