@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=2)
+    ap.add_argument("--ulysses-heads-per-step", type=int, default=1,
+                    help="workload 4 on several GPUs: heads per pipelined exchange/compute step")
     ap.add_argument("--quick", action="store_true", help="device-resident arm only (for profiler runs)")
     return ap.parse_args()
 
@@ -207,7 +209,8 @@ def main():
         assert N % world == 0 and H % world == 0
         n_loc = N // world
         q, k, v = (t[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous() for t in (q, k, v))
-        api = lambda a, b, c: ulysses_attention(a, b, c, topk=topk, is_causal=causal, pvthreshd=args.pvthreshd)
+        api = lambda a, b, c: ulysses_attention(a, b, c, topk=topk, is_causal=causal, pvthreshd=args.pvthreshd,
+                                                heads_per_step=args.ulysses_heads_per_step)
     else:
         api = lambda a, b, c: S.spas_sage2_attn_meansim_topk_cuda(a, b, c, topk=topk, is_causal=causal,
                                                                  pvthreshd=args.pvthreshd)
@@ -250,6 +253,9 @@ def main():
                               "warmup": args.warmup, "ms_per_step": ms_step, "quick": True,
                               "config": config_dict(idx, w, topk, world, ulysses)}))
         if dist is not None:
+            if ulysses:
+                from spargeattn_b200.sharding import close_peer_exchanges
+                close_peer_exchanges()
             dist.destroy_process_group()
         return
 
@@ -371,6 +377,9 @@ def main():
                 "cpu_baseline": cpu_baseline}
         print(json.dumps(line))
     if dist is not None:
+        if ulysses:
+            from spargeattn_b200.sharding import close_peer_exchanges
+            close_peer_exchanges()
         dist.destroy_process_group()
 
 

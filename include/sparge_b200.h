@@ -164,6 +164,22 @@ int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_int8, const u
  * The reference has no counterpart (its sm90 kernel spins without a limit, qk_int_sv_f8_cuda_sm90.cuh:117-132). */
 int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int slice_ns, unsigned int slices, sparge_stream_t stream);
 
+/* Peer-memory buffers for the sequence-parallel (Ulysses) exchange of workload 4; no counterpart in the
+ * reference, whose multi-GPU runs go through xfuser / torch.distributed outside its attention package
+ * (inference_examples/wan_infer.py). One process per GPU: sparge_peer_alloc makes a device buffer and a
+ * 64-byte handle that other processes of the same node pass to sparge_peer_open to map that buffer
+ * (peer access is enabled on first use); sparge_copy_async / sparge_copy2d_async are one copy-engine transfer
+ * each (contiguous / `height` rows of `width` bytes with pitches) between any two device pointers, local or mapped. sparge_peer_alloc / _open / _close / _free synchronise the device and are
+ * meant to run once, at set-up and tear-down; only the two copy calls belong on the data path. The owner must
+ * keep a buffer alive until every peer has closed its mapping. */
+int sparge_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int sparge_peer_free(void* ptr);
+int sparge_peer_open(const unsigned char* handle64, void** ptr);
+int sparge_peer_close(void* ptr);
+int sparge_copy_async(void* dst, const void* src, size_t bytes, sparge_stream_t stream);
+int sparge_copy2d_async(void* dst, size_t dpitch, const void* src, size_t spitch, size_t width, size_t height,
+                        sparge_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

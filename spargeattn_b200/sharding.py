@@ -9,7 +9,8 @@ Two schemes, both outside the kernels:
   into all N tokens of H/G heads, the single-GPU path runs unchanged, and a second all-to-all
   returns the output to the sequence-sharded layout.  Pooling and quantisation happen after the
   exchange on full-length heads, so results are identical to a single-GPU run.  The received
-  chunks land in this GPU's own memory before any kernel reads them.
+  chunks land in this GPU's own memory before any kernel reads them.  `ulysses_attention` does the
+  exchanges head by head on a second stream so that they overlap the attention of the other heads.
 """
 from typing import Callable, List, Optional, Sequence
 
@@ -56,19 +57,270 @@ def head_to_seq_shard(x: torch.Tensor, group=None) -> torch.Tensor:
     return recv.permute(1, 0, 2, 3, 4).reshape(B, G * h, N // G, D).contiguous()
 
 
+def _exchange(send_chunks, recv_chunks, group) -> None:
+    """Chunk g of `send_chunks` goes to rank g of the group; chunk s of `recv_chunks` comes from rank s.
+    All chunks are contiguous tensors of one size: nothing is staged, the data lands where it is used."""
+    G = dist.get_world_size(group)
+    r = dist.get_rank(group)
+    recv_chunks[r].copy_(send_chunks[r])
+    ops = []
+    for g in range(G):
+        if g == r:
+            continue
+        peer = dist.get_global_rank(group, g) if group is not None else g
+        ops.append(dist.P2POp(dist.isend, send_chunks[g], peer, group))
+        ops.append(dist.P2POp(dist.irecv, recv_chunks[g], peer, group))
+    for req in dist.batch_isend_irecv(ops) if ops else []:
+        req.wait()
+
+
+class PeerExchange:
+    """Per-rank exchange buffers that the other ranks of a single-node group map into their address space
+    (CUDA IPC through the C ABI's sparge_peer_* calls), so that the sequence<->head exchanges become
+    copy-engine transfers over NVLink: ranks pull their heads' token slices out of the peers' input buffers
+    and push output slices into the peers' output buffers. No SM is used by the transfers, so they overlap
+    the attention kernels; the only collectives left are two one-element all-reduces per call that order
+    the copies across ranks (everyone has staged / everyone has pushed).
+
+    Collective: every rank of `group` must construct it, call `ensure` with the same sizes, and `close`."""
+
+    def __init__(self, group=None):
+        import ctypes
+        from . import _cabi
+        self._ct, self._lib, self._check = ctypes, _cabi.lib, _cabi.check
+        self.group = group
+        self.G = dist.get_world_size(group)
+        self.r = dist.get_rank(group)
+        self.in_bytes = self.out_bytes = 0
+        self.local_in = self.local_out = None
+        self.peer_in = {}
+        self.peer_out = {}
+        self.flag = None
+
+    def _alloc(self, nbytes):
+        ptr, handle = self._ct.c_void_p(), self._ct.create_string_buffer(64)
+        self._check(self._lib.sparge_peer_alloc(nbytes, self._ct.byref(ptr), handle), "sparge_peer_alloc")
+        return ptr.value, handle.raw
+
+    def _open_all(self, handle):
+        handles = [None] * self.G
+        dist.all_gather_object(handles, handle, group=self.group)
+        mapped = {}
+        for s in range(self.G):
+            if s != self.r:
+                p = self._ct.c_void_p()
+                self._check(self._lib.sparge_peer_open(handles[s], self._ct.byref(p)), "sparge_peer_open")
+                mapped[s] = p.value
+        return mapped
+
+    def ensure(self, in_bytes: int, out_bytes: int, device) -> None:
+        if in_bytes <= self.in_bytes and out_bytes <= self.out_bytes:
+            return
+        self.close()
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.local_in, h_in = self._alloc(in_bytes)
+        self.local_out, h_out = self._alloc(out_bytes)
+        self.peer_in = self._open_all(h_in)
+        self.peer_out = self._open_all(h_out)
+        self.in_bytes, self.out_bytes = in_bytes, out_bytes
+
+    def fence(self) -> None:
+        """Stream-ordered rendezvous of all ranks on the current stream."""
+        dist.all_reduce(self.flag, group=self.group)
+
+    def copy(self, dst, src, nbytes, stream) -> None:
+        self._check(self._lib.sparge_copy_async(dst, src, nbytes, stream.cuda_stream), "sparge_copy_async")
+
+    def copy2d(self, dst, dpitch, src, spitch, width, height, stream) -> None:
+        self._check(self._lib.sparge_copy2d_async(dst, dpitch, src, spitch, width, height, stream.cuda_stream),
+                    "sparge_copy2d_async")
+
+    def close(self) -> None:
+        """Unmap the peers' buffers, wait until every rank has done so, then free this rank's buffers."""
+        if self.local_in is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for table in (self.peer_in, self.peer_out):
+            for p in table.values():
+                self._lib.sparge_peer_close(p)
+            table.clear()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self._lib.sparge_peer_free(self.local_in)
+        self._lib.sparge_peer_free(self.local_out)
+        self.local_in = self.local_out = None
+        self.in_bytes = self.out_bytes = 0
+
+
+_PEER_EXCHANGES = {}
+
+
+def peer_exchange(group=None) -> PeerExchange:
+    """The process-wide PeerExchange of a group (created on first use by every rank)."""
+    key = id(group) if group is not None else None
+    if key not in _PEER_EXCHANGES:
+        _PEER_EXCHANGES[key] = PeerExchange(group)
+    return _PEER_EXCHANGES[key]
+
+
+def close_peer_exchanges() -> None:
+    """Collective tear-down of every PeerExchange; call before destroying the process group."""
+    for ex in _PEER_EXCHANGES.values():
+        ex.close()
+    _PEER_EXCHANGES.clear()
+
+
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attention: Optional[Callable] = None,
-                      group=None, **kwargs) -> torch.Tensor:
+                      group=None, heads_per_step: int = 1, exchange: str = "auto", **kwargs) -> torch.Tensor:
     """Sequence-parallel wrapper: q, k, v are [B, H, N/G, D] shards; returns the [B, H, N/G, D] output shard.
-    `attention` defaults to spas_sage2_attn_meansim_topk_cuda; per-head knobs given as [H] tensors are sliced."""
+    `attention` defaults to spas_sage2_attn_meansim_topk_cuda; per-head knobs given as [H] tensors are sliced.
+
+    The H/G heads a rank owns are processed `heads_per_step` at a time. On CUDA the exchanges run on a second
+    stream: while the attention of one step runs, the inputs of the next step arrive and the output of the
+    previous step leaves, so only the first input exchange and the last output exchange are exposed. Every
+    exchange writes straight into its final place ([N, D] per head going in, the caller-layout shard coming
+    back); no permuted staging copies are made.
+
+    `exchange`: "peer" moves the data with copy-engine transfers between IPC-mapped buffers (PeerExchange; one
+    node, NCCL group, CUDA tensors), "p2p" with batched send/recv of the process group (any backend);
+    "auto" picks "peer" for CUDA tensors on an NCCL group and "p2p" otherwise."""
     if attention is None:
         from .core import spas_sage2_attn_meansim_topk_cuda as attention
     G = dist.get_world_size(group)
     r = dist.get_rank(group)
-    H = q.shape[1]
+    B, H, n, D = q.shape
+    assert H % G == 0, "number of heads must be divisible by the sequence-parallel size"
     hs = H // G
-    for name, val in list(kwargs.items()):
-        if isinstance(val, torch.Tensor) and val.dim() == 1 and val.numel() == H:
-            kwargs[name] = val[r * hs:(r + 1) * hs]
-    qh, kh, vh = (seq_to_head_shard(t, group) for t in (q, k, v))
-    oh = attention(qh, kh, vh, **kwargs)
-    return head_to_seq_shard(oh.contiguous(), group)
+    step = max(1, min(int(heads_per_step), hs))
+    q, k, v = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
+    out = torch.empty_like(q)
+    cuda = q.is_cuda
+    if exchange == "auto":
+        exchange = "peer" if (cuda and dist.get_backend(group) == "nccl") else "p2p"
+    if exchange not in ("peer", "p2p"):
+        raise ValueError("exchange must be 'auto', 'peer' or 'p2p'")
+    if exchange == "peer" and not cuda:
+        raise ValueError("exchange='peer' needs CUDA tensors")
+    main = torch.cuda.current_stream(q.device) if cuda else None
+    steps = [(j0, min(j0 + step, hs)) for j0 in range(0, hs, step)]
+    full = [tuple(torch.empty(B, j1 - j0, G * n, D, dtype=t.dtype, device=t.device) for t in (q, k, v))
+            for (j0, j1) in steps]
+    outs = [None] * len(steps)
+    ev_in = [torch.cuda.Event() if cuda else None for _ in steps]
+
+    def exchange_in(i):
+        j0, j1 = steps[i]
+        for src, dst in zip((q, k, v), full[i]):
+            for b in range(B):
+                for j in range(j0, j1):
+                    _exchange([src[b, g * hs + j] for g in range(G)],
+                              [dst[b, j - j0, s * n:(s + 1) * n] for s in range(G)], group)
+
+    def exchange_out(i):
+        j0, j1 = steps[i]
+        o = outs[i]
+        for b in range(B):
+            for j in range(j0, j1):
+                _exchange([o[b, j - j0, s * n:(s + 1) * n] for s in range(G)],
+                          [out[b, g * hs + j] for g in range(G)], group)
+
+    if exchange == "peer":
+        px = peer_exchange(group)
+        es = q.element_size()
+        shard = B * H * n * D * es                     # one tensor's shard on one rank
+        px.ensure(3 * shard, shard, q.device)
+        row, full_row = n * D * es, G * n * D * es     # one head's token slice / one full-length head
+
+        def exchange_in(i, stream):                    # noqa: F811 - replaces the send/recv version
+            j0, j1 = steps[i]
+            for t, (src, dst) in enumerate(zip((q, k, v), full[i])):
+                for b in range(B):
+                    head0 = ((b * H) + r * hs + j0) * row
+                    for s_ in range(G):
+                        base = src.data_ptr() if s_ == r else px.peer_in[s_] + t * shard
+                        px.copy2d(dst.data_ptr() + b * (j1 - j0) * full_row + s_ * row, full_row,
+                                  base + head0, row, row, j1 - j0, stream)
+
+        def exchange_out(i, stream):                   # noqa: F811
+            j0, j1 = steps[i]
+            o = outs[i]
+            for b in range(B):
+                head0 = ((b * H) + r * hs + j0) * row
+                for s_ in range(G):
+                    base = px.local_out if s_ == r else px.peer_out[s_]
+                    px.copy2d(base + head0, row, o.data_ptr() + b * (j1 - j0) * full_row + s_ * row, full_row,
+                              row, j1 - j0, stream)
+    else:
+        px = None
+        _in, _out = exchange_in, exchange_out
+        exchange_in = lambda i, stream=None: _in(i)
+        exchange_out = lambda i, stream=None: _out(i)
+
+    def head_kwargs(i):
+        j0, j1 = steps[i]
+        kw = dict(kwargs)
+        for name, val in kwargs.items():
+            if isinstance(val, torch.Tensor) and val.dim() == 1 and val.numel() == H:
+                kw[name] = val[r * hs + j0:r * hs + j1]
+        return kw
+
+    if not cuda:
+        for i in range(len(steps)):
+            exchange_in(i)
+            outs[i] = attention(*full[i], **head_kwargs(i)).contiguous()
+            exchange_out(i)
+        return out
+
+    # Streams: `comm` carries every exchange; the attention of step i runs on compute stream i % 2, so the
+    # last CTAs of one step and the first CTAs of the next share the SMs instead of leaving them idle.
+    work = _side_streams(q.device)
+    comm, compute = work[0], work[1:]
+    comm.wait_stream(main)                      # inputs and the buffers above are ready
+    for cs in compute:
+        cs.wait_stream(main)
+    with torch.cuda.stream(comm):
+        if px is not None:
+            # stage my shards where the peers can read them; nobody pulls before everybody has staged
+            for t, src in enumerate((q, k, v)):
+                px.copy(px.local_in + t * shard, src.data_ptr(), shard, comm)
+            px.fence()
+        exchange_in(0, comm)
+        ev_in[0].record(comm)
+        if len(steps) > 1:
+            exchange_in(1, comm)
+            ev_in[1].record(comm)
+    for i in range(len(steps)):
+        cs = compute[i % len(compute)]
+        with torch.cuda.stream(cs):
+            cs.wait_event(ev_in[i])
+            o = attention(*full[i], **head_kwargs(i))
+            outs[i] = o if o.is_contiguous() else o.contiguous()
+            outs[i].record_stream(comm)
+            done = torch.cuda.Event()
+            done.record(cs)
+        with torch.cuda.stream(comm):
+            comm.wait_event(done)
+            exchange_out(i, comm)
+            if i + 2 < len(steps):
+                exchange_in(i + 2, comm)
+                ev_in[i + 2].record(comm)
+    if px is not None:
+        with torch.cuda.stream(comm):
+            px.fence()                                 # every rank's pushes have landed
+            px.copy(out.data_ptr(), px.local_out, shard, comm)
+    main.wait_stream(comm)
+    for cs in compute:
+        main.wait_stream(cs)
+    return out
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_streams(device):
+    """One exchange stream and two compute streams per device, created once."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = [torch.cuda.Stream(device=key, priority=-1)] + [torch.cuda.Stream(device=key) for _ in range(2)]
+    return _SIDE_STREAMS[key]

@@ -47,6 +47,8 @@ def _worker(rank, world, port, q, k, v, topk, out_dict):
     hs = q.shape[1] // world
     assert torch.equal(qh, q[:, rank * hs:(rank + 1) * hs])
     o = ulysses_attention(qs, ks, vs, attention=_ref_attention, topk=topk)
+    o2 = ulysses_attention(qs, ks, vs, attention=_ref_attention, topk=topk, heads_per_step=2)
+    assert torch.equal(o, o2)
     out_dict[rank] = o
     dist.barrier()
     dist.destroy_process_group()
