@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=2)
-    ap.add_argument("--ulysses-heads-per-step", type=int, default=1,
+    ap.add_argument("--ulysses-heads-per-step", type=int, default=None,
                     help="workload 4 on several GPUs: heads per pipelined exchange/compute step")
     ap.add_argument("--quick", action="store_true", help="device-resident arm only (for profiler runs)")
     return ap.parse_args()

@@ -172,11 +172,11 @@ def close_peer_exchanges() -> None:
 
 
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attention: Optional[Callable] = None,
-                      group=None, heads_per_step: int = 1, exchange: str = "auto", **kwargs) -> torch.Tensor:
+                      group=None, heads_per_step: Optional[int] = None, exchange: str = "auto", **kwargs) -> torch.Tensor:
     """Sequence-parallel wrapper: q, k, v are [B, H, N/G, D] shards; returns the [B, H, N/G, D] output shard.
     `attention` defaults to spas_sage2_attn_meansim_topk_cuda; per-head knobs given as [H] tensors are sliced.
 
-    The H/G heads a rank owns are processed `heads_per_step` at a time. On CUDA the exchanges run on a second
+    The H/G heads a rank owns are processed `heads_per_step` at a time (None: chosen from the problem size). On CUDA the exchanges run on a second
     stream: while the attention of one step runs, the inputs of the next step arrive and the output of the
     previous step leaves, so only the first input exchange and the last output exchange are exposed. Every
     exchange writes straight into its final place ([N, D] per head going in, the caller-layout shard coming
@@ -192,6 +192,12 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
     B, H, n, D = q.shape
     assert H % G == 0, "number of heads must be divisible by the sequence-parallel size"
     hs = H // G
+    if heads_per_step is None:
+        # Smallest step whose attention launch still fills the GPU for about a dozen waves of CTAs (two per SM):
+        # shorter launches lose more to their partial last wave than the extra overlap gains.
+        slots = 2 * torch.cuda.get_device_properties(q.device).multi_processor_count if q.is_cuda else 1
+        per_head = B * ((G * n + 127) // 128)
+        heads_per_step = next((c for c in range(1, hs + 1) if c * per_head >= 12 * slots), hs)
     step = max(1, min(int(heads_per_step), hs))
     q, k, v = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
     out = torch.empty_like(q)
@@ -242,6 +248,18 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
                         px.copy2d(dst.data_ptr() + b * (j1 - j0) * full_row + s_ * row, full_row,
                                   base + head0, row, row, j1 - j0, stream)
 
+        def stage(i, stream):
+            """Copy the slices that the peers will pull for their step i into my exchange buffer."""
+            if i >= len(steps):
+                return
+            j0, j1 = steps[i]
+            for t, src in enumerate((q, k, v)):
+                for b in range(B):
+                    for s_ in range(G):
+                        if s_ != r:
+                            ofs = ((b * H) + s_ * hs + j0) * row
+                            px.copy(px.local_in + t * shard + ofs, src.data_ptr() + ofs, (j1 - j0) * row, stream)
+
         def exchange_out(i, stream):                   # noqa: F811
             j0, j1 = steps[i]
             o = outs[i]
@@ -281,12 +299,16 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
         cs.wait_stream(main)
     with torch.cuda.stream(comm):
         if px is not None:
-            # stage my shards where the peers can read them; nobody pulls before everybody has staged
-            for t, src in enumerate((q, k, v)):
-                px.copy(px.local_in + t * shard, src.data_ptr(), shard, comm)
+            # stage the slices of the first step where the peers can read them; nobody pulls a slice before
+            # every rank has staged it (one-element all-reduce = stream-ordered rendezvous)
+            stage(0, comm)
             px.fence()
         exchange_in(0, comm)
         ev_in[0].record(comm)
+        if px is not None and len(steps) > 1:
+            for i in range(1, len(steps)):
+                stage(i, comm)
+            px.fence()
         if len(steps) > 1:
             exchange_in(1, comm)
             ev_in[1].record(comm)
