@@ -158,10 +158,9 @@ _PEER_EXCHANGES = {}
 
 def peer_exchange(group=None) -> PeerExchange:
     """The process-wide PeerExchange of a group (created on first use by every rank)."""
-    key = id(group) if group is not None else None
-    if key not in _PEER_EXCHANGES:
-        _PEER_EXCHANGES[key] = PeerExchange(group)
-    return _PEER_EXCHANGES[key]
+    if group not in _PEER_EXCHANGES:            # keyed by the group object itself (None = default group)
+        _PEER_EXCHANGES[group] = PeerExchange(group)
+    return _PEER_EXCHANGES[group]
 
 
 def close_peer_exchanges() -> None:
