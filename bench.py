@@ -387,7 +387,7 @@ def main():
 # quant_v (3, plus one memset), attention (1)
 GPU_LAUNCHES_PER_STEP = 9
 # dram bytes (read + write) of one attention launch, from the ncu capture summarised under profiles/
-ATTN_DRAM_TRAFFIC_BYTES = {2: 155731456 + 70603520}   # profiles/attn_kernel_cfg2_wan480p.md
+ATTN_DRAM_TRAFFIC_BYTES = {2: 154650112 + 70302464}   # profiles/attn_kernel_cfg2_wan480p.md
 
 if __name__ == "__main__":
     main()
