@@ -182,8 +182,9 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
     back); no permuted staging copies are made.
 
     `exchange`: "peer" moves the data with copy-engine transfers between IPC-mapped buffers (PeerExchange; one
-    node, NCCL group, CUDA tensors), "p2p" with batched send/recv of the process group (any backend);
-    "auto" picks "peer" for CUDA tensors on an NCCL group and "p2p" otherwise."""
+    node, NCCL group, CUDA tensors), "p2p" with batched send/recv of the process group (any backend), "a2a"
+    with one all_to_all_single per tensor and no pipelining; "auto" picks "peer" for CUDA tensors on an NCCL
+    group and "p2p" otherwise."""
     if attention is None:
         from .core import spas_sage2_attn_meansim_topk_cuda as attention
     G = dist.get_world_size(group)
@@ -203,8 +204,14 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
     cuda = q.is_cuda
     if exchange == "auto":
         exchange = "peer" if (cuda and dist.get_backend(group) == "nccl") else "p2p"
+    if exchange == "a2a":                          # one all-to-all per tensor, nothing pipelined
+        for name, val in list(kwargs.items()):
+            if isinstance(val, torch.Tensor) and val.dim() == 1 and val.numel() == H:
+                kwargs[name] = val[r * hs:(r + 1) * hs]
+        qh, kh, vh = (seq_to_head_shard(t, group) for t in (q, k, v))
+        return head_to_seq_shard(attention(qh, kh, vh, **kwargs).contiguous(), group)
     if exchange not in ("peer", "p2p"):
-        raise ValueError("exchange must be 'auto', 'peer' or 'p2p'")
+        raise ValueError("exchange must be 'auto', 'peer', 'p2p' or 'a2a'")
     if exchange == "peer" and not cuda:
         raise ValueError("exchange='peer' needs CUDA tensors")
     main = torch.cuda.current_stream(q.device) if cuda else None
@@ -237,15 +244,36 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
         px.ensure(3 * shard, shard, q.device)
         row, full_row = n * D * es, G * n * D * es     # one head's token slice / one full-length head
 
+        # Transfers with different peers go to different streams, so that several copy engines and all the
+        # NVLink ports work at once; `stream` (the exchange stream) forks to the lanes and joins them again.
+        lanes = _side_streams(q.device)[3:]
+
+        def fork(stream):
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            for lane in lanes:
+                lane.wait_event(ev)
+
+        def join(stream):
+            for lane in lanes:
+                ev = torch.cuda.Event()
+                ev.record(lane)
+                stream.wait_event(ev)
+
+        def lane_of(s_, stream):
+            return stream if s_ == r else lanes[s_ % len(lanes)]
+
         def exchange_in(i, stream):                    # noqa: F811 - replaces the send/recv version
             j0, j1 = steps[i]
+            fork(stream)
             for t, (src, dst) in enumerate(zip((q, k, v), full[i])):
                 for b in range(B):
                     head0 = ((b * H) + r * hs + j0) * row
                     for s_ in range(G):
                         base = src.data_ptr() if s_ == r else px.peer_in[s_] + t * shard
                         px.copy2d(dst.data_ptr() + b * (j1 - j0) * full_row + s_ * row, full_row,
-                                  base + head0, row, row, j1 - j0, stream)
+                                  base + head0, row, row, j1 - j0, lane_of(s_, stream))
+            join(stream)
 
         def stage(i, stream):
             """Copy the slices that the peers will pull for their step i into my exchange buffer."""
@@ -253,6 +281,9 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
                 return
             j0, j1 = steps[i]
             for t, src in enumerate((q, k, v)):
+                if len(steps) == 1:                    # everything at once: one copy per tensor
+                    px.copy(px.local_in + t * shard, src.data_ptr(), shard, stream)
+                    continue
                 for b in range(B):
                     for s_ in range(G):
                         if s_ != r:
@@ -262,12 +293,14 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
         def exchange_out(i, stream):                   # noqa: F811
             j0, j1 = steps[i]
             o = outs[i]
+            fork(stream)
             for b in range(B):
                 head0 = ((b * H) + r * hs + j0) * row
                 for s_ in range(G):
                     base = px.local_out if s_ == r else px.peer_out[s_]
                     px.copy2d(base + head0, row, o.data_ptr() + b * (j1 - j0) * full_row + s_ * row, full_row,
-                              row, j1 - j0, stream)
+                              row, j1 - j0, lane_of(s_, stream))
+            join(stream)
     else:
         px = None
         _in, _out = exchange_in, exchange_out
@@ -292,7 +325,7 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
     # Streams: `comm` carries every exchange; the attention of step i runs on compute stream i % 2, so the
     # last CTAs of one step and the first CTAs of the next share the SMs instead of leaving them idle.
     work = _side_streams(q.device)
-    comm, compute = work[0], work[1:]
+    comm, compute = work[0], work[1:3]
     comm.wait_stream(main)                      # inputs and the buffers above are ready
     for cs in compute:
         cs.wait_stream(main)
@@ -340,8 +373,8 @@ _SIDE_STREAMS = {}
 
 
 def _side_streams(device):
-    """One exchange stream and two compute streams per device, created once."""
+    """One exchange stream, two compute streams and four transfer lanes per device, created once."""
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     if key not in _SIDE_STREAMS:
-        _SIDE_STREAMS[key] = [torch.cuda.Stream(device=key, priority=-1)] + [torch.cuda.Stream(device=key) for _ in range(2)]
+        _SIDE_STREAMS[key] = [torch.cuda.Stream(device=key, priority=-1)] + [torch.cuda.Stream(device=key) for _ in range(6)]
     return _SIDE_STREAMS[key]
