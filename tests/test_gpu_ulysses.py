@@ -46,7 +46,7 @@ def _worker(rank, world, port, heads_per_step, exchange, result):
 
 
 @pytest.mark.parametrize("exchange", ["peer", "p2p", "a2a"])
-@pytest.mark.parametrize("heads_per_step", [1, 3, 4])
+@pytest.mark.parametrize("heads_per_step", [1, 4])
 def test_ulysses_two_gpus_equals_single_gpu(heads_per_step, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
