@@ -49,6 +49,8 @@ def _worker(rank, world, port, q, k, v, topk, out_dict):
     o = ulysses_attention(qs, ks, vs, attention=_ref_attention, topk=topk)
     o2 = ulysses_attention(qs, ks, vs, attention=_ref_attention, topk=topk, heads_per_step=2)
     assert torch.equal(o, o2)
+    o3 = ulysses_attention(qs, ks, vs, attention=_ref_attention, topk=topk, exchange="a2a")
+    assert torch.allclose(o, o3, atol=1e-6)
     out_dict[rank] = o
     dist.barrier()
     dist.destroy_process_group()
