@@ -57,8 +57,8 @@ int sparge_k_mean(const void* k, void* km, void* scratch, int B, int H, int N, i
  *
  *   - Requests needing more scratch than the array holds return SPARGE_ERR_TOO_LARGE:
  *     sparge_k_mean_scratch_bytes(B,H,N,D) = B*H*ceil(N/512)*D*8 must be <= the maximum.
- *   - The first call on each device looks up the array's device address (no allocation). Make that
- *     first call outside any stream capture, with the intended device current.
+ *   - The first call on each device looks up the array's device address (no allocation); make every call
+ *     with the intended device current.
  *   - All calls on a device share the one array, and it keeps whatever the previous call left in it.
  *     The kernels overwrite every element they later read, so no clearing is needed, but two calls
  *     whose kernels can overlap on the GPU (different streams, no dependency) race on it: order them.
