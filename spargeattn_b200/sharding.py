@@ -205,7 +205,7 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
     if exchange == "auto":
         # Measured on B200 (workload of 119 056 tokens, 24 heads): on 2 GPUs the pipelined peer exchange wins
         # (31.3 ms against 35.1 for "a2a"); on 8 GPUs, 3 heads per rank leave nothing to pipeline and the plain
-        # all-to-all was the fastest measured (8.96 ms against 9.26 for "peer" on one transfer lane).
+        # all-to-all was the fastest measured (8.89 ms against 9.06 for "peer" and 9.07 for "p2p").
         if cuda and dist.get_backend(group) == "nccl":
             exchange = "peer" if G == 2 else "a2a"
         else:
