@@ -64,8 +64,9 @@ def dense_equiv_ops(B, H, N, D, causal):
 
 def config_dict(idx, w, topk, n_gpus, ulysses=False):
     B, H, N, D = workload_shape(w)
-    sharding = (f"Ulysses sequence parallel over {n_gpus} GPUs: N/{n_gpus} tokens per rank, NCCL all-to-all to "
-                f"{H // n_gpus} heads per rank and back (strong scaling)") if ulysses else \
+    sharding = (f"Ulysses sequence parallel over {n_gpus} GPUs: N/{n_gpus} tokens per rank, exchanged to "
+                f"{H // n_gpus} full-length heads per rank and back ("
+                f"{'pipelined copy-engine peer transfers' if n_gpus == 2 else 'NCCL all-to-all'}; strong scaling)") if ulysses else \
         f"{n_gpus} x full head set (weak scaling, no collective)"
     return {"workload": f"cfg{idx}:{w['name']} B={B} H={H} N={N} D={D} bf16 {'causal' if w['causal'] else 'non-causal'} "
                         f"topk={topk} pvthreshd={PVTHRESHD:g}",
@@ -198,6 +199,7 @@ def main():
     # workload 4 on several GPUs: Ulysses sequence parallelism (strong scaling, two all-to-alls per call);
     # every other case: each rank runs the full head set on its own data (weak scaling, no collective)
     ulysses = world > 1 and w.get("ulysses", False)
+    calls_per_step = 1
     gen_seed_shift = 0 if ulysses else rank
     if w["kind"] == "llm":
         q, k, v = synthetic.llm_prefill_qkv(B, H, N, D, idx + 100 * gen_seed_shift, dev)
@@ -209,6 +211,10 @@ def main():
         assert N % world == 0 and H % world == 0
         n_loc = N // world
         q, k, v = (t[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous() for t in (q, k, v))
+        if world == 2:      # peer exchange: one attention call per group of heads
+            from spargeattn_b200.sharding import auto_heads_per_step
+            hstep = args.ulysses_heads_per_step or auto_heads_per_step(B, N, H // world, dev)
+            calls_per_step = -(-(H // world) // hstep)
         api = lambda a, b, c: ulysses_attention(a, b, c, topk=topk, is_causal=causal, pvthreshd=args.pvthreshd,
                                                 heads_per_step=args.ulysses_heads_per_step)
     else:
@@ -373,7 +379,7 @@ def main():
                 "config": config_dict(idx, w, topk, world, ulysses), "clocks": clk.summary(),
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": in_bytes,
                         "d2h_bytes_per_step": out_bytes},
-                "gpu_launches": GPU_LAUNCHES_PER_STEP * args.steps, "roofline": roofline, "kernels": kernels,
+                "gpu_launches": GPU_LAUNCHES_PER_STEP * args.steps * calls_per_step, "roofline": roofline, "kernels": kernels,
                 "cpu_baseline": cpu_baseline}
         print(json.dumps(line))
     if dist is not None:

@@ -170,6 +170,15 @@ def close_peer_exchanges() -> None:
     _PEER_EXCHANGES.clear()
 
 
+def auto_heads_per_step(B: int, N: int, heads: int, device) -> int:
+    """Smallest step whose attention launch still fills the GPU for about a dozen waves of CTAs (two per SM):
+    shorter launches lose more to their partial last wave than the extra overlap gains."""
+    device = torch.device(device)
+    slots = 2 * torch.cuda.get_device_properties(device).multi_processor_count if device.type == "cuda" else 1
+    per_head = B * ((N + 127) // 128)
+    return next((c for c in range(1, heads + 1) if c * per_head >= 12 * slots), heads)
+
+
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attention: Optional[Callable] = None,
                       group=None, heads_per_step: Optional[int] = None, exchange: str = "auto", **kwargs) -> torch.Tensor:
     """Sequence-parallel wrapper: q, k, v are [B, H, N/G, D] shards; returns the [B, H, N/G, D] output shard.
@@ -193,11 +202,7 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
     assert H % G == 0, "number of heads must be divisible by the sequence-parallel size"
     hs = H // G
     if heads_per_step is None:
-        # Smallest step whose attention launch still fills the GPU for about a dozen waves of CTAs (two per SM):
-        # shorter launches lose more to their partial last wave than the extra overlap gains.
-        slots = 2 * torch.cuda.get_device_properties(q.device).multi_processor_count if q.is_cuda else 1
-        per_head = B * ((G * n + 127) // 128)
-        heads_per_step = next((c for c in range(1, hs + 1) if c * per_head >= 12 * slots), hs)
+        heads_per_step = auto_heads_per_step(B, G * n, hs, q.device)
     step = max(1, min(int(heads_per_step), hs))
     q, k, v = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
     out = torch.empty_like(q)
