@@ -164,7 +164,17 @@ int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_int8, const u
  * The reference has no counterpart (its sm90 kernel spins without a limit, qk_int_sv_f8_cuda_sm90.cuh:117-132). */
 int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int slice_ns, unsigned int slices, sparge_stream_t stream);
 
-/* Peer-memory buffers for the sequence-parallel (Ulysses) exchange of workload 4; no counterpart in the
+/* Sustained rate of the 8-bit tensor pipe, measured on the current device: the denominator of the attention
+ * kernel's roofline. No counterpart in the reference (it ships no benchmark). Every CTA keeps a 128 x 128-byte
+ * A tile and an n x 128-byte B tile in shared memory and one thread issues `iters` x 4 tcgen05.mma
+ * (M = 128, N = n, K = 32) back to back. kind 0 = kind::i8, 1 = kind::f8f6f4; n in {64, 128, 256};
+ * ctas_per_sm in {1, 2} (two issuing threads per SM, as the attention kernel has). Launches a warm-up and a
+ * timed run on `stream`, waits for them, and returns the timed run's milliseconds and its operation count
+ * (2 per multiply-add). Creates two CUDA events; allocates no device memory. */
+int sparge_tensor_peak(int kind, int n, int ctas_per_sm, int iters, int32_t* dev_status, float* ms_out, double* ops_out,
+                       sparge_stream_t stream);
+
+/* Peer-memory buffers for a sequence-parallel (Ulysses) exchange between the GPUs of one node; no counterpart in the
  * reference, whose multi-GPU runs go through xfuser / torch.distributed outside its attention package
  * (inference_examples/wan_infer.py). One process per GPU: sparge_peer_alloc makes a device buffer and a
  * 64-byte handle that other processes of the same node pass to sparge_peer_open to map that buffer

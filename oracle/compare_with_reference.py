@@ -1,0 +1,232 @@
+"""Side-by-side run of this library and the compiled reference on one CUDA device.  TEST INFRASTRUCTURE.
+
+    python oracle/compare_with_reference.py [--cases small,cfg0,cfg1,cfg2,cfg3,cfg4] [--time] [--out report.json]
+
+For every case both implementations get the same q, k, v.  Reported per case:
+  * mismatch counts of every bit-exact quantity (K mean, pooled values, self-similarity flags, INT8 Q/K,
+    scales, block map, LUT, counts, FP8 V bytes, V scales) -- the reference leaves several summation
+    orders and division instructions to Triton / cuBLAS / --use_fast_math, so these counts are measured,
+    not assumed to be zero;
+  * how many blocks of the reference's own map flip when its unstable sort (utils.py:397) is left alone;
+  * attention parity in the reference's metric (utils.py:25-36): this library's kernel against the
+    reference kernel on the *reference's* quantised operands and LUT (arithmetic only), and whole API
+    against whole API;
+  * with --time, latency of both public entry points (CUDA events).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+sys.path.insert(0, HERE)
+import ref_runner as RR  # noqa: E402
+
+RR.load()                                   # the reference takes the name spas_sage_attn first
+sys.path.insert(0, ROOT)
+import spargeattn_b200 as S  # noqa: E402
+from spargeattn_b200 import ops, synthetic  # noqa: E402
+import sparge_oracle as O  # noqa: E402
+
+
+def small_inputs(B, H, N, D, dtype, seed):
+    """The generator of tests/test_gpu_attention.py: N(0,1) plus a slow random walk, K with a channel bias."""
+    g = torch.Generator().manual_seed(seed)
+    walk = lambda: torch.cumsum(torch.randn(B, H, N, D, generator=g), dim=2) * 0.1
+    q = (torch.randn(B, H, N, D, generator=g) + walk()).to(dtype)
+    k = (torch.randn(B, H, N, D, generator=g) + walk() + torch.randn(D, generator=g) * 3).to(dtype)
+    v = (torch.randn(B, H, N, D, generator=g) + walk()).to(dtype)
+    return q, k, v
+
+
+def _neq(a, b) -> int:
+    return int((a != b).sum().item())
+
+
+def _bits(t):
+    return t.view(torch.int16) if t.dtype in (torch.float16, torch.bfloat16) else t
+
+
+def metric(a, b) -> dict:
+    """utils.py:25-36 on the device, in fp64 chunks (b is the reference)."""
+    a, b = a.reshape(-1), b.reshape(-1)
+    dot = na = nb = l1 = ref = 0.0
+    for i in range(0, a.numel(), 1 << 26):
+        x, y = a[i:i + (1 << 26)].double(), b[i:i + (1 << 26)].double()
+        dot += float((x * y).sum())
+        na += float((x * x).sum())
+        nb += float((y * y).sum())
+        l1 += float((x - y).abs().sum())
+        ref += float(y.abs().sum())
+    return {"Cossim": dot / max((na * nb) ** 0.5, 1e-300), "L1": l1 / max(ref, 1e-300)}
+
+
+def compare(q, k, v, is_causal=False, topk=0.5, simthreshd1=-0.1, attention_sink=False, pvthreshd=50.0,
+            cdfthreshd=None) -> dict:
+    """q, k, v: CUDA tensors [B,H,N,D] of one 16-bit dtype."""
+    B, H, N, D = q.shape
+    dev = q.device
+    rep = {"shape": [B, H, N, D], "dtype": str(q.dtype).replace("torch.", ""), "causal": bool(is_causal),
+           "topk": topk, "cdfthreshd": cdfthreshd}
+    # ---------------------------------------------------------------- reference
+    rq, rk, rv16, rkm = RR.prologue(q, k, v)
+    rp = RR.predictor(rq, rk, rkm, is_causal, simthreshd1, cdfthreshd, topk, attention_sink, stable=True)
+    rp_unstable = RR.predictor(rq, rk, rkm, is_causal, simthreshd1, cdfthreshd, topk, attention_sink, stable=False)
+    rep["ref_tie_flips_blocks"] = _neq(rp["map"], rp_unstable["map"])
+    del rp_unstable
+    r_v8, r_vs, r_v8_tok = RR.quant_v(rv16)
+    pv_t = torch.full((H,), float(pvthreshd), dtype=torch.float32, device=dev)
+    sm = D ** -0.5
+    r_o = RR.attention(rp["q_int8"], rp["k_int8"], r_v8, rp["lut"], rp["valid"], pv_t, rp["q_scale"], rp["k_scale"],
+                       r_vs, sm, q.dtype)
+    # ---------------------------------------------------------------- this library, step by step
+    km = ops.k_mean(k)
+    thr = torch.full((H,), float(simthreshd1), dtype=torch.float32, device=dev)
+    pq, sq, q8, qs = ops.pool_sim_quant(q, None, 128, thr)
+    pk, sk, k8, ks = ops.pool_sim_quant(k, km, 64, thr)
+    tk = None if topk is None else torch.full((H,), float(topk), dtype=torch.float32, device=dev)
+    cdf = None if cdfthreshd is None else torch.full((H,), float(cdfthreshd), dtype=torch.float32, device=dev)
+    lut, valid, fmap = ops.select_blocks(pq, pk, sq, sk, tk, cdf, is_causal, attention_sink, want_mask=True)
+    v8, vs = ops.quant_v(v)
+    pv_arg = pv_t if pvthreshd < 30 else None
+    o = ops.attn_fwd(q8, k8, v8, lut, valid, pv_arg, qs, ks, vs, sm, False, q.dtype)
+    # ---------------------------------------------------------------- bit-exact quantities
+    nq, nk = fmap.shape[-2:]
+    rep["elements"] = B * H * N * D
+    rep["blocks"] = B * H * nq * nk
+    rep["km_neq"] = _neq(_bits(km), _bits(rkm))
+    d8q = (q8.int() - rp["q_int8"].int()).abs()
+    d8k = (k8.int() - rp["k_int8"].int()).abs()
+    rep["q_int8_neq"], rep["q_int8_maxdiff"] = int((d8q != 0).sum()), int(d8q.max())
+    rep["k_int8_neq"], rep["k_int8_maxdiff"] = int((d8k != 0).sum()), int(d8k.max())
+    rep["q_scale_neq"], rep["k_scale_neq"] = _neq(qs, rp["q_scale"]), _neq(ks, rp["k_scale"])
+    rep["q_scale_maxrel"] = float(((qs - rp["q_scale"]).abs() / rp["q_scale"]).max())
+    rep["k_scale_maxrel"] = float(((ks - rp["k_scale"]).abs() / rp["k_scale"]).max())
+    rep["pooled_q_neq"], rep["pooled_k_neq"] = _neq(_bits(pq), _bits(rp["pq"])), _neq(_bits(pk), _bits(rp["pk"]))
+    rep["sim_q_neq"], rep["sim_k_neq"] = _neq(sq.bool(), rp["sim_q"]), _neq(sk.bool(), rp["sim_k"])
+    rep["map_neq"] = _neq(fmap.bool(), rp["map"])
+    rep["map_rows_neq"] = int((fmap.bool() != rp["map"]).any(-1).sum())
+    rep["valid_neq"] = _neq(valid, rp["valid"])
+    rep["lut_neq"] = _neq(lut, rp["lut"])
+    rep["live_blocks"] = int(rp["valid"].sum())
+    # this library's selection kernel fed the reference's own pooled values and flags: isolates the selection rule
+    lut2, valid2, fmap2 = ops.select_blocks(rp["pq"], rp["pk"], rp["sim_q"].to(torch.uint8), rp["sim_k"].to(torch.uint8),
+                                            tk, cdf, is_causal, attention_sink, want_mask=True)
+    rep["map_neq_given_ref_pools"] = _neq(fmap2.bool(), rp["map"])
+    l3, v3 = ops.mask_to_lut(rp["map"])
+    rep["lut_of_ref_map_neq"] = _neq(l3, rp["lut"]) + _neq(v3, rp["valid"])
+    rep["v8_neq"] = _neq(v8, r_v8_tok)
+    rep["v_scale_neq"] = _neq(vs, r_vs)
+    rep["v_scale_maxrel"] = float(((vs - r_vs).abs() / r_vs.abs().clamp(min=1e-30)).max())
+    # ---------------------------------------------------------------- attention parity
+    o_arith = ops.attn_fwd(rp["q_int8"], rp["k_int8"], r_v8_tok, rp["lut"], rp["valid"], pv_arg, rp["q_scale"],
+                           rp["k_scale"], r_vs, sm, False, q.dtype)
+    rep["attn_same_operands"] = metric(o_arith, r_o)
+    rep["attn_whole_path"] = metric(o, r_o)
+    r_api = RR.api_topk(q, k, v, stable=True, topk=topk, is_causal=is_causal, simthreshd1=simthreshd1,
+                        attention_sink=attention_sink, pvthreshd=pvthreshd) if cdfthreshd is None else None
+    if r_api is not None:
+        o_api = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=topk, is_causal=is_causal, simthreshd1=simthreshd1,
+                                                    attention_sink=attention_sink, pvthreshd=pvthreshd)
+        rep["api_vs_api"] = metric(o_api, r_api)
+    ops.check_device_status(dev)
+    return rep
+
+
+def oracle_vs_reference(q, k, v, is_causal, topk, simthreshd1=-0.1, attention_sink=False, cdfthreshd=None) -> dict:
+    """CPU oracle against the reference's device results (small cases only)."""
+    rq, rk, rv16, rkm = RR.prologue(q, k, v)
+    rp = RR.predictor(rq, rk, rkm, is_causal, simthreshd1, cdfthreshd, topk, attention_sink, stable=True)
+    _, r_vs, r_v8_tok = RR.quant_v(rv16)
+    qc, kc, vc = q.cpu(), k.cpu(), v.cpu()
+    km = O.k_mean(kc)
+    pr = O.predictor(qc, kc, km, is_causal, simthreshd1, cdfthreshd, topk, attention_sink)
+    v8, vs = O.quant_v(vc)
+    return {"km_neq": _neq(_bits(km), _bits(rkm.cpu())), "q_int8_neq": _neq(pr["q_int8"], rp["q_int8"].cpu()),
+            "k_int8_neq": _neq(pr["k_int8"], rp["k_int8"].cpu()), "q_scale_neq": _neq(pr["q_scale"], rp["q_scale"].cpu()),
+            "k_scale_neq": _neq(pr["k_scale"], rp["k_scale"].cpu()), "map_neq": _neq(pr["map"], rp["map"].cpu()),
+            "pooled_q_neq": _neq(_bits(pr["pq"]), _bits(rp["pq"].cpu())),
+            "pooled_k_neq": _neq(_bits(pr["pk"]), _bits(rp["pk"].cpu())),
+            "v8_neq": _neq(O.e4m3_bits(v8), r_v8_tok.cpu()), "v_scale_neq": _neq(vs, r_vs.cpu())}
+
+
+SMALL = [(1, 2, 128, 64), (1, 2, 200, 128), (2, 2, 640, 64), (1, 2, 1000, 128), (1, 2, 3000, 64), (1, 1, 8200, 128)]
+# workload index -> (heads compared, extra sequence lengths cut from the same tensors)
+FULL = {0: (4, []), 1: (4, [17550]), 2: (4, []), 3: (4, []), 4: (2, [119040])}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--cases", default="small,cfg0,cfg1,cfg2,cfg3,cfg4")
+    ap.add_argument("--time", action="store_true")
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args()
+    want = a.cases.split(",")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    report = {"cases": [], "timing": []}
+    if "small" in want:
+        for n, shape in enumerate(SMALL):
+            for dtype in (torch.bfloat16, torch.float16):
+                causal = n % 2 == 1
+                q, k, v = (t.to(dev) for t in small_inputs(*shape, dtype, 10))
+                r = compare(q, k, v, is_causal=causal, topk=0.5, simthreshd1=0.2)
+                r["case"] = "small"
+                r["oracle_vs_ref"] = oracle_vs_reference(q, k, v, causal, 0.5, simthreshd1=0.2)
+                report["cases"].append(r)
+                print(json.dumps(r), flush=True)
+        q, k, v = (t.to(dev) for t in small_inputs(1, 2, 5000, 128, torch.bfloat16, 11))
+        r = compare(q, k, v, topk=None, cdfthreshd=0.9, simthreshd1=0.3)
+        r["case"] = "small-cdf"
+        report["cases"].append(r)
+        print(json.dumps(r), flush=True)
+    for idx, (heads, extra) in FULL.items():
+        if f"cfg{idx}" not in want:
+            continue
+        w = synthetic.WORKLOADS[idx]
+        q, k, v = synthetic.workload_qkv(idx, dev, heads=heads)
+        topks = [0.3, 0.5, 0.7] if idx == 2 else [w["topk"]]
+        for n_cut in [None] + extra:
+            qq, kk, vv = (t if n_cut is None else t[:, :, :n_cut].contiguous() for t in (q, k, v))
+            for tk in topks:
+                r = compare(qq, kk, vv, is_causal=w["causal"], topk=tk)
+                r["case"] = f"cfg{idx}"
+                report["cases"].append(r)
+                print(json.dumps(r), flush=True)
+            if idx == 2 and n_cut is None:
+                r = compare(qq, kk, vv, is_causal=False, topk=0.5, pvthreshd=5.0)
+                r["case"] = "cfg2-pv5"
+                report["cases"].append(r)
+                print(json.dumps(r), flush=True)
+        del q, k, v
+        torch.cuda.empty_cache()
+        if a.time:
+            q, k, v = synthetic.workload_qkv(idx, dev)
+            B, H, N, D = q.shape
+            for tk in topks:
+                kw = dict(topk=tk, is_causal=w["causal"])
+                t_ref = RR.time_ms(lambda: RR.api_topk(q, k, v, stable=False, **kw))
+                t_our = RR.time_ms(lambda: S.spas_sage2_attn_meansim_topk_cuda(q, k, v, **kw))
+                ops_ = 4.0 * B * H * N * N * D * (0.5 if w["causal"] else 1.0)
+                row = {"case": f"cfg{idx}", "shape": [B, H, N, D], "topk": tk, "reference_ms": t_ref, "ours_ms": t_our,
+                       "reference_TOPS": ops_ / t_ref / 1e9, "ours_TOPS": ops_ / t_our / 1e9}
+                if idx == 1:
+                    mask = synthetic.bernoulli_block_mask(B, H, N, 0.4, 1, dev)
+                    row["block_sparse_reference_ms"] = RR.time_ms(lambda: RR.api_block_sparse(q, k, v, mask))
+                    row["block_sparse_ours_ms"] = RR.time_ms(lambda: S.block_sparse_sage2_attn_cuda(q, k, v, mask_id=mask))
+                report["timing"].append(row)
+                print(json.dumps(row), flush=True)
+            del q, k, v
+            torch.cuda.empty_cache()
+    if a.out:
+        os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)
+        json.dump(report, open(a.out, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -288,13 +288,15 @@ def quant_v(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
 # ----------------------------------------------------------------------------- attention
 def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_scale: float, pvthreshd,
-                        token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True):
+                        token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True, q_blocks=None):
     """Oracle B: block-online emulation of csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:42-755 with the
     helpers of csrc/qattn/attn_utils.cuh (update_mo :418-466, exponentiate_r :391-415,
     RS_32_to_8 :581-596, normalize_d :757-811).  fp32 PV accumulation.
 
     q8,k8: int8 [B,H,N,D]; q_scale [B,H,nq]; k_scale [B,H,nk]; v8: e4m3 values fp32 [B,H,N_pad,D];
-    v_scale [B,H,D]; block_map bool [B,H,nq,nk]; pvthreshd fp32 [H]."""
+    v_scale [B,H,D]; block_map bool [B,H,nq,nk]; pvthreshd fp32 [H].
+    `q_blocks`: optional list of query-block indices; only those 128-row blocks are evaluated (the other
+    rows of the result stay zero), so that a sample of a long sequence can be checked in seconds."""
     B, H, N, D = q8.shape
     nq, nk = block_map.shape[-2:]
     c = sm_scale * LOG2E
@@ -303,7 +305,7 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
     for b in range(B):
         for h in range(H):
             kf = k8[b, h].float()
-            for i in range(nq):
+            for i in (range(nq) if q_blocks is None else q_blocks):
                 r0, r1 = i * BLKQ, min((i + 1) * BLKQ, N)
                 qf = q8[b, h, r0:r1].float()
                 rows = r1 - r0
@@ -338,6 +340,73 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
                 if live:
                     o[b, h, r0:r1] = acc / d.unsqueeze(-1) * v_scale[b, h].view(1, D)
     return o.to(out_dtype), skipped
+
+
+def attention_blockwise_sampled(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_scale: float, pvthreshd,
+                                q_blocks, token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True):
+    """`attention_blockwise` restricted to the query blocks in `q_blocks`, evaluated for all (batch, head,
+    query block) samples at once: the loop runs over the position in each sample's live list, not over
+    samples, so a few dozen blocks of a 100k-token sequence take seconds.  Same arithmetic, same visiting
+    order (ascending key block), same skip rule.  Returns [B,H,len(q_blocks)*128,D] (rows beyond N are zero)
+    and the number of skipped blocks."""
+    B, H, N, D = q8.shape
+    nq, nk = block_map.shape[-2:]
+    c = sm_scale * LOG2E
+    qb = torch.as_tensor(list(q_blocks), dtype=torch.long)
+    nb = qb.numel()
+    S = B * H * nb
+    bi = torch.arange(B).view(B, 1, 1).expand(B, H, nb).reshape(S)
+    hi = torch.arange(H).view(1, H, 1).expand(B, H, nb).reshape(S)
+    qi = qb.view(1, 1, nb).expand(B, H, nb).reshape(S)
+    pad_q = nq * BLKQ - N
+    q8p = torch.cat([q8, torch.zeros(B, H, pad_q, D, dtype=q8.dtype)], 2) if pad_q else q8
+    pad_k = nk * BLKK - N
+    k8p = torch.cat([k8, torch.zeros(B, H, pad_k, D, dtype=k8.dtype)], 2) if pad_k else k8
+    v8p = v8 if v8.shape[2] >= nk * BLKK else torch.cat([v8, torch.zeros(B, H, nk * BLKK - v8.shape[2], D)], 2)
+    qf = q8p.view(B, H, nq, BLKQ, D)[bi, hi, qi].float()                      # [S,128,D]
+    kblk = k8p.view(B, H, nk, BLKK, D)
+    vblk = v8p[:, :, :nk * BLKK].reshape(B, H, nk, BLKK, D)
+    bm = block_map[bi, hi, qi]                                                # [S,nk]
+    cnt = bm.sum(-1)
+    order = torch.sort(torch.where(bm, torch.arange(nk).expand(S, nk), torch.arange(nk).expand(S, nk) + nk), dim=-1).values
+    qrow = qi.view(S, 1) * BLKQ + torch.arange(BLKQ).view(1, BLKQ)             # [S,128]
+    row_ok = qrow < N
+    qsc = q_scale[bi, hi, qi]
+    thr = pvthreshd[hi]
+    m = torch.full((S, BLKQ), MASK_VALUE, dtype=torch.float32)
+    d = torch.ones(S, BLKQ, dtype=torch.float32)
+    acc = torch.zeros(S, BLKQ, D, dtype=torch.float32)
+    skipped = 0
+    for n_it in range(int(cnt.max()) if S else 0):
+        act = n_it < cnt
+        j = torch.where(act, order[:, n_it], torch.zeros_like(cnt))
+        s = torch.matmul(qf, kblk[bi, hi, j].float().transpose(-1, -2))        # exact: |S| < 2^24
+        t = s * (c * qsc * k_scale[bi, hi, j]).view(S, 1, 1)
+        kidx = j.view(S, 1) * BLKK + torch.arange(BLKK).view(1, BLKK)          # [S,64]
+        dead = (kidx >= N).view(S, 1, BLKK)
+        if token_causal:
+            dead = dead | (kidx.view(S, 1, BLKK) > qrow.view(S, BLKQ, 1))
+        t = torch.where(dead, torch.full_like(t, MASK_VALUE), t)
+        rowmax = t.amax(dim=-1)
+        m_new = torch.maximum(m, rowmax)
+        upd = act.clone()
+        if pv_skip:
+            delta = torch.where(row_ok, rowmax - m, torch.full_like(m, float("-inf"))).amax(dim=-1)
+            skip = act & (n_it < cnt - 2) & (delta + thr <= 0)
+            skipped += int(skip.sum())
+            upd = upd & ~skip
+        alpha = torch.exp2(m - m_new)
+        p = torch.exp2(t - m_new.unsqueeze(-1) + S_FP8_OFFSET)
+        p = torch.where(dead, torch.zeros_like(p), p)
+        d_new = d * alpha + p.sum(dim=-1)
+        acc_new = acc * alpha.unsqueeze(-1) + torch.matmul(e4m3_round(p), vblk[bi, hi, j])
+        u1, u2 = upd.view(S, 1), upd.view(S, 1, 1)
+        m = torch.where(u1, m_new, m)
+        d = torch.where(u1, d_new, d)
+        acc = torch.where(u2, acc_new, acc)
+    o = acc / d.unsqueeze(-1) * v_scale[bi, hi].view(S, 1, D)
+    o = torch.where((row_ok & (cnt > 0).view(S, 1)).unsqueeze(-1), o, torch.zeros_like(o))
+    return o.view(B, H, nb * BLKQ, D).to(out_dtype), skipped
 
 
 def attention_dense_masked(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_scale: float,

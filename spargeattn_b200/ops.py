@@ -157,3 +157,26 @@ def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale,
                                                    float(sm_scale), out.stride(0), out.stride(1), out.stride(2),
                                                    _ptr(pv_count), _stream(q8)), "sparge_attn_fwd")
     return (out, pv_count) if return_pv_count else out
+
+
+def tensor_peak(kind: str = "i8", n: int = 128, ctas_per_sm: int = 2, target_ms: float = 50.0, device=None) -> dict:
+    """Sustained tcgen05.mma rate of the current device for 8-bit operands (M = 128, N = n, K = 32 per
+    instruction, operands resident in shared memory): {"tops", "ms", "kind", "n", "ctas_per_sm"}.
+    A first short run sizes the timed one to about `target_ms`."""
+    import ctypes
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    code = {"i8": 0, "f8": 1}[kind]
+    status = device_status_word(dev)
+    ms, nops = ctypes.c_float(), ctypes.c_double()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def run(iters):
+        _cabi.check(_cabi.lib.sparge_tensor_peak(code, n, ctas_per_sm, iters, _ptr(status), ctypes.byref(ms),
+                                                 ctypes.byref(nops), stream), "sparge_tensor_peak")
+        return float(ms.value), float(nops.value)
+
+    with torch.cuda.device(dev):
+        t, _ = run(4096)
+        iters = int(max(4096, min(1 << 22, 4096 * target_ms / max(t, 1e-3))))
+        t, total = run(iters)
+    return {"tops": total / (t * 1e-3) / 1e12, "ms": t, "kind": kind, "n": n, "ctas_per_sm": ctas_per_sm}

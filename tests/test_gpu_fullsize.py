@@ -74,3 +74,157 @@ def test_bounded_wait_reports_expiry_and_context_survives():
     assert _cabi.lib.sparge_selftest_wait_expiry(status.data_ptr(), 1000000000, 1000, stream) == _cabi.ERR_INVALID_ARG
     x = torch.arange(8, device="cuda").sum().item()                       # the context is still usable
     assert x == 28
+
+
+# --------------------------------------------------------------------------------------------------
+# Parity at the benchmark workloads' own sizes (bf16), two heads each:
+#   * every integer / byte / index quantity bit-exact against the oracle (K mean, INT8 Q/K, scales, pooled
+#     values, self-similarity flags, FP8 V, V scales, block map, LUT, counts);
+#   * attention output of the public API against the oracle's block-online emulation at the same mask on
+#     a sample of query blocks (the first 8, the last 8 including a partial one, 16 random ones), at the
+#     tolerance the attention tests use everywhere: cosine >= 0.999, relative L1 <= 1e-2.
+# The oracle evaluates a two-head slice of these shapes in seconds; the sampled rows keep its Python
+# block loop short.
+COS_MIN, L1_MAX = 0.999, 1e-2
+
+
+def _sample_blocks(nq, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    mid = (torch.randperm(max(nq - 16, 1), generator=g)[:16] + 8).tolist() if nq > 16 else []
+    return sorted(set(list(range(min(8, nq))) + list(range(max(0, nq - 8), nq)) + mid))
+
+
+def _bits16(t):
+    return t.view(torch.int16)
+
+
+def _oracle_front(q, k, v):
+    """Everything of the oracle that does not depend on the selection knobs."""
+    H = q.shape[1]
+    thr = torch.full((H,), -0.1)
+    km = O.k_mean(k)
+    pq, sim_q, q8, qs = O.pool_sim_quant(q, None, 128, thr)
+    pk, sim_k, k8, ks = O.pool_sim_quant(k, km, 64, thr)
+    v8, vs = O.quant_v(v)
+    return dict(km=km, pq=pq, pk=pk, sim_q=sim_q, sim_k=sim_k, q8=q8, qs=qs, k8=k8, ks=ks, v8=v8, vs=vs, thr=thr)
+
+
+def _gpu_front_bit_exact(qc, kc, vc, fr):
+    """Runs the preprocessing kernels and asserts bit equality with the oracle; returns the device tensors."""
+    from spargeattn_b200 import ops
+    km = ops.k_mean(kc)
+    assert torch.equal(_bits16(km.cpu()), _bits16(fr["km"])), "K mean differs"
+    thr = fr["thr"].cuda()
+    pq, sq, q8, qs = ops.pool_sim_quant(qc, None, 128, thr)
+    pk, sk, k8, ks = ops.pool_sim_quant(kc, km, 64, thr)
+    for name, got, want in (("q_int8", q8, fr["q8"]), ("k_int8", k8, fr["k8"]), ("q_scale", qs, fr["qs"]),
+                            ("k_scale", ks, fr["ks"])):
+        n = int((got.cpu() != want).sum())
+        assert n == 0, f"{name}: {n} of {want.numel()} elements differ"
+    for name, got, want in (("pooled_q", pq, fr["pq"]), ("pooled_k", pk, fr["pk"])):
+        n = int((_bits16(got.cpu()) != _bits16(want)).sum())
+        assert n == 0, f"{name}: {n} of {want.numel()} values differ"
+    assert torch.equal(sq.cpu().bool(), fr["sim_q"]) and torch.equal(sk.cpu().bool(), fr["sim_k"]), "sim flags differ"
+    v8, vs = ops.quant_v(vc)
+    n = int((v8.cpu() != O.e4m3_bits(fr["v8"])).sum())
+    assert n == 0, f"fp8 V: {n} of {v8.numel()} bytes differ"
+    assert torch.equal(vs.cpu(), fr["vs"]), "V scales differ"
+    return dict(pq=pq, pk=pk, sq=sq, sk=sk)
+
+
+def _select_bit_exact(dev, fr, topk, causal):
+    from spargeattn_b200 import ops
+    H = fr["pq"].shape[1]
+    tk = torch.full((H,), float(topk))
+    p = O.pooled_probs(fr["pq"], fr["pk"], fr["sim_k"], causal)
+    fmap = O.select_blocks(p, fr["sim_q"], fr["sim_k"], tk, None, causal, False)
+    lut_o, valid_o = O.block_map_to_lut(fmap)
+    lut, valid, mask = ops.select_blocks(dev["pq"], dev["pk"], dev["sq"], dev["sk"], tk.cuda(), None, causal, False,
+                                         want_mask=True)
+    n = int((mask.cpu().bool() != fmap).sum())
+    assert n == 0, f"block map: {n} of {fmap.numel()} blocks differ (topk {topk})"
+    assert torch.equal(valid.cpu(), valid_o) and torch.equal(lut.cpu(), lut_o), "LUT / counts differ"
+    return fmap
+
+
+def _attention_on_sample(o_gpu, fr, fmap, D, pvthreshd, token_causal, blocks):
+    H, N = fr["q8"].shape[1], fr["q8"].shape[2]
+    pv = O.hyperparameter_check(float(pvthreshd), H)
+    o_ref, _ = O.attention_blockwise_sampled(fr["q8"], fr["qs"], fr["k8"], fr["ks"], fr["v8"], fr["vs"], fmap, D ** -0.5,
+                                             pv, blocks, token_causal, torch.bfloat16)
+    B = o_ref.shape[0]
+    pad = (-N) % 128
+    og = torch.nn.functional.pad(o_gpu.float().cpu(), (0, 0, 0, pad)).view(B, H, -1, 128, D)[:, :, blocks].reshape(o_ref.shape)
+    m = O.precision_metric(og, o_ref.float())
+    assert m["Cossim"] >= COS_MIN and m["L1"] <= L1_MAX, m
+    return m
+
+
+def _workload_inputs(idx, heads, n_cut=None):
+    from spargeattn_b200 import synthetic
+    q, k, v = synthetic.workload_qkv(idx, "cpu", heads=heads)
+    if n_cut is not None:
+        q, k, v = (t[:, :, :n_cut].contiguous() for t in (q, k, v))
+    return q, k, v
+
+
+@pytest.mark.parametrize("idx,n_cut,topks,pvs", [
+    (1, None, (0.5,), (50.0,)),             # CogVideoX shape, N = 226 + 13*30*45 = 17776, D = 64, B = 2
+    (1, 17550, (0.5,), (50.0,)),            # the same tensors cut to 17550 tokens: partial last block on both sides
+    (2, None, (0.3, 0.5, 0.7), (50.0, 5.0)),   # Wan 480p shape, N = 32760, D = 128
+    (3, None, (0.5,), (50.0,)),             # causal prefill shape, N = 32768, D = 128
+    (4, None, (0.4,), (50.0,)),             # HunyuanVideo shape, N = 119056: nk = 1861 (selection kernel's large-row path)
+    (4, 119040, (0.4,), (50.0,)),
+])
+def test_workload_sizes_bit_exact_preprocessing_and_sampled_attention(idx, n_cut, topks, pvs):
+    import spargeattn_b200 as S
+    from spargeattn_b200 import ops, synthetic
+    w = synthetic.WORKLOADS[idx]
+    causal = w["causal"]
+    q, k, v = _workload_inputs(idx, 2, n_cut)
+    B, H, N, D = q.shape
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    fr = _oracle_front(q, k, v)
+    dev = _gpu_front_bit_exact(qc, kc, vc, fr)
+    blocks = _sample_blocks((N + 127) // 128, seed=idx)
+    for topk in topks:
+        fmap = _select_bit_exact(dev, fr, topk, causal)
+        for pv in (pvs if topk == w["topk"] else pvs[:1]):
+            o = S.spas_sage2_attn_meansim_topk_cuda(qc, kc, vc, topk=topk, is_causal=causal, pvthreshd=pv)
+            ops.check_device_status()
+            m = _attention_on_sample(o, fr, fmap, D, pv, False, blocks)
+            print(f"workload {idx} N={N} topk={topk} pvthreshd={pv}: cos {m['Cossim']:.6f} relL1 {m['L1']:.5f}")
+        if causal:       # the Sage1-signature entry point masks key > query inside the kernel as well
+            o = S.spas_sage_attn_meansim_topk_cuda(qc, kc, vc, topk=topk, is_causal=True)
+            ops.check_device_status()
+            _attention_on_sample(o, fr, fmap, D, 50.0, True, blocks[:12])
+
+
+@pytest.mark.parametrize("n_cut", [None, 17550])
+def test_cogvideox_size_block_sparse_api_with_bernoulli_mask(n_cut):
+    """block_sparse_sage2_attn_cuda at the CogVideoX shape with a Bernoulli(0.4) per-head block mask whose diagonal
+    blocks are forced live: quantiser-only INT8 path, mask -> LUT and attention, all at full sequence length."""
+    import spargeattn_b200 as S
+    from spargeattn_b200 import ops, synthetic
+    q, k, v = _workload_inputs(1, 2, n_cut)
+    B, H, N, D = q.shape
+    mask = synthetic.bernoulli_block_mask(B, H, N, 0.4, seed=1)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    km = O.k_mean(k)
+    dummy = torch.zeros(H)
+    _, _, q8, qs = O.pool_sim_quant(q, None, 128, dummy, want_pool=False)
+    _, _, k8, ks = O.pool_sim_quant(k, km, 64, dummy, want_pool=False)
+    v8, vs = O.quant_v(v)
+    kmg = ops.k_mean(kc)
+    _, _, q8g, qsg = ops.pool_sim_quant(qc, None, 128, None)
+    _, _, k8g, ksg = ops.pool_sim_quant(kc, kmg, 64, None)
+    assert torch.equal(q8g.cpu(), q8) and torch.equal(k8g.cpu(), k8) and torch.equal(qsg.cpu(), qs) and torch.equal(ksg.cpu(), ks)
+    lut_o, valid_o = O.block_map_to_lut(mask)
+    lut, valid = ops.mask_to_lut(mask.cuda())
+    assert torch.equal(lut.cpu(), lut_o) and torch.equal(valid.cpu(), valid_o)
+    o, sp = S.block_sparse_sage2_attn_cuda(qc, kc, vc, mask_id=mask.cuda(), return_sparsity=True)
+    ops.check_device_status()
+    nq, nk = mask.shape[-2:]
+    assert abs(sp - (1.0 - float(valid_o.sum()) / ((nk + 2) // 2 * nq * B * H))) < 1e-6     # core.py:229-231
+    fr = dict(q8=q8, qs=qs, k8=k8, ks=ks, v8=v8, vs=vs)
+    _attention_on_sample(o, fr, mask != 0, D, 50.0, False, _sample_blocks(nq, seed=7))

@@ -105,3 +105,26 @@ def test_sparsity_formulas():
     mask = torch.ones(1, 2, 8, 16, dtype=torch.int32)
     _, sp = O.block_sparse_sage2_attn(q, k, v, mask, return_sparsity=True, blockwise=False)
     assert abs(sp - (1 - 16 * 8 * 2 / ((16 + 2) // 2 * 8 * 2))) < 1e-6     # core.py:229-231 denominator
+
+
+@pytest.mark.parametrize("shape,causal,pv,gain", [((1, 2, 1000, 64), False, 50.0, 1.0), ((2, 2, 1100, 128), True, 50.0, 1.0),
+                                                  ((1, 2, 2048, 64), False, 4.0, 3.0)])
+def test_sampled_blockwise_attention_equals_the_block_loop(shape, causal, pv, gain):
+    """The batched evaluation used for long sequences is the same arithmetic as the per-block loop."""
+    B, H, N, D = shape
+    g = torch.Generator().manual_seed(14)
+    walk = lambda: torch.cumsum(torch.randn(B, H, N, D, generator=g), dim=2) * 0.1
+    q = ((torch.randn(B, H, N, D, generator=g) + walk()) * gain).bfloat16()
+    k = (torch.randn(B, H, N, D, generator=g) + walk() + torch.randn(D, generator=g) * 3).bfloat16()
+    v = (torch.randn(B, H, N, D, generator=g) + walk()).bfloat16()
+    pr = O.predictor(q, k, O.k_mean(k), causal, -0.1, None, 0.6, False)
+    v8, vs = O.quant_v(v)
+    pvt = O.hyperparameter_check(pv, H)
+    blocks = list(range((N + 127) // 128))[::2]
+    args = (pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v8, vs, pr["map"], D ** -0.5, pvt)
+    o1, s1 = O.attention_blockwise(*args, causal, torch.float32, q_blocks=blocks)
+    o2, s2 = O.attention_blockwise_sampled(*args, blocks, causal, torch.float32)
+    assert s1 == s2 and (pv > 30 or s1 > 0)
+    pad = (-N) % 128
+    o1b = torch.nn.functional.pad(o1, (0, 0, 0, pad)).view(B, H, -1, 128, D)[:, :, blocks].reshape(o2.shape)
+    assert torch.allclose(o1b, o2, rtol=1e-5, atol=1e-6)
