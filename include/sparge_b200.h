@@ -105,10 +105,17 @@ int sparge_mask_to_lut(const void* mask, int elem_size, int32_t* lut, int32_t* v
  * (csrc/fused/fused.cu:193-267) and scale_fuse_quant_cuda (fused.cu:269-344).
  *   v [B,H,N,D] (16-bit; bf16 is rounded to fp16 first, as the reference does)
  *   -> v8 [B,H,N_pad,D] e4m3 bytes, token-major, rows >= N zero; v_scale [B,H,D] fp32.
+ *   v_scale = amax * RN(1/2.25) and v8 = e4m3(v * div.approx(2.25, amax)): the reference's fast-math quotients.
  *   The reference's [B,H,D,N_pad] transposition and 16-token permutation are layout artefacts
  *   of its mma.sync operand registers and are not reproduced. */
 int sparge_quant_v(const void* v, uint8_t* v8, float* v_scale, int B, int H, int N, int D, int dtype,
                    sparge_stream_t stream);
+
+/* out[i] = a[i] / b[i] as `div.approx.ftz.f32` evaluates it on this GPU: the approximate quotient that the
+ * reference's V quantiser uses (csrc/fused/fused.cu:150,163 compiled with --use_fast_math, setup.py:60) and that
+ * sparge_quant_v reproduces. The hardware reciprocal has no published bit-level definition, so a CPU restatement
+ * of the V quantiser takes this function's output as an input. Test support; a, b, out are device pointers. */
+int sparge_div_approx(const float* a, const float* b, float* out, int n, sparge_stream_t stream);
 
 /* LUT-driven block-sparse attention: INT8 QK^T and FP8 PV on tcgen05 tensor cores.
  * Replaces qk_int8_sv_f8_accum_f16_block_sparse_attn_inst_buf_fuse_v_scale_with_pv_threshold

@@ -5,10 +5,16 @@ This module restates, in plain PyTorch on the CPU, the arithmetic of the referen
 the smoke check and the CPU-baseline leg of the benchmark may import it; the product
 (`spargeattn_b200`) never does and fails loudly without its CUDA library.
 
-Parity status: **parity unpinned**.  The reference ships no tests, golden vectors or stored
-input/output pairs for this path, and its own kernels need a GPU, so this restatement is
-pinned only against (a) the reference's Triton kernels run under the Triton CPU interpreter
-for fp16 inputs (tests/golden/make_golden.py records those fixtures) and (b) itself.
+Parity status: the reference ships no tests, golden vectors or stored input/output pairs for this
+path, so this restatement is pinned against outputs of the reference itself instead:
+  (a) the compiled reference (oracle/build_ref.py) run on a B200 by tests/golden/make_ref_gpu_golden.py:
+      fixtures tests/golden/ref_gpu_*.pt in bf16 and fp16 hold its K mean, pooled values, flags, INT8 Q/K,
+      scales, block map, LUT, counts, FP8 V bytes and V scales, and its attention output;
+  (b) the reference's Triton kernels run under the Triton CPU interpreter for fp16 inputs
+      (tests/golden/make_golden.py, fixtures ref_predictor_*.pt).
+tests/test_oracle_golden.py states what is bit-exact against (a) and (b) and bounds the rest (pooled
+values can differ in the last bit of a handful of entries because the compiled kernel's reduction
+order is Triton's own; the attention output is compared at cosine >= 0.999, relative L1 <= 1e-2).
 
 Where the reference leaves a summation order or a division instruction to a library
 (Triton reductions, cuBLAS, torch softmax/sort), this file pins one choice, stated at each
@@ -17,7 +23,14 @@ bit for bit:
   * the K mean and the softmax accumulate in fp64 (order-free to ~1e-16) and are rounded to
     fp32 once; block pooling and row norms use short fp32 running sums in a fixed order,
     combined in fp64 / by a fixed butterfly (see pool_sim_quant);
-  * fp32 divisions are IEEE round-to-nearest;
+  * the Q/K block scale is fma(max|x|, RN(1/127), 1e-7) -- the compiled reference contracts
+    `max / 127. + 1e-7` that way (bit-exact on every fixture scale); the element quotient x / scale
+    is IEEE (the reference's approximate quotient gave the same INT8 on every compared element);
+  * the V scale is amax * RN(1/2.25) and the V multiplier 2.25 * (1 / amax): csrc/fused is built with
+    --use_fast_math, i.e. dividend times the hardware reciprocal of the divisor. The hardware
+    reciprocal has no published bit-level definition: `quant_v` takes the device's value as an
+    optional input and otherwise uses the correctly rounded reciprocal (differs from the device
+    in about 2 of 10^4 FP8 bytes);
   * the pooled score is an fp32 FMA chain over ascending channel index;
   * the row softmax is evaluated in fp64, rounded to fp32, then to the 16-bit dtype;
   * top-k uses a stable descending order (ties -> lower block index).
@@ -87,6 +100,26 @@ def e4m3_from_bits(b: torch.Tensor) -> torch.Tensor:
     return b.view(torch.float8_e4m3fn).to(torch.float32)
 
 
+def fma_f32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
+    """Correctly rounded fp32 fused multiply-add a * b + c (one rounding), elementwise.
+    The product of two fp32 numbers is exact in fp64; the fp64 sum is made exact with a two-sum error
+    term, which decides the (rare) case where the fp64 sum lands on an fp32 rounding midpoint."""
+    p = a.double() * b.double()
+    cd = c.double().expand_as(p)
+    s = p + cd
+    bb = s - p
+    err = (p - (s - bb)) + (cd - bb)                       # s + err == p + c exactly
+    r = s.float()
+    rd = r.double()
+    up = torch.nextafter(r, torch.full_like(r, float("inf"))).double()
+    dn = torch.nextafter(r, torch.full_like(r, float("-inf"))).double()
+    tie_up = (s - rd == (up - rd) / 2) & (s > rd)          # s exactly half way towards the next fp32
+    tie_dn = (rd - s == (rd - dn) / 2) & (s < rd)
+    r = torch.where(tie_up & (err > 0), up.float(), r)     # true sum above the midpoint: round up
+    r = torch.where(tie_dn & (err < 0), dn.float(), r)
+    return r
+
+
 # ----------------------------------------------------------------------------- K mean
 def k_mean(k: torch.Tensor) -> torch.Tensor:
     """spas_sage_attn/core.py:119-120 `km = k.mean(dim=-2, keepdim=True)` in k's dtype.
@@ -124,9 +157,9 @@ def pool_sim_quant(x: torch.Tensor, km: Optional[torch.Tensor], bs: int, simthre
         xb = torch.where(valid.view(1, 1, nb, bs, 1), xb, torch.zeros((), dtype=x.dtype))
     x32 = xb.float()
 
-    # utils.py:206-210 -- scale = max|x| / 127 + 1e-7 ; round half away from zero
+    # utils.py:206-210 -- scale = max|x| / 127 + 1e-7 (one FMA in the compiled kernel); round half away from zero
     amax = x32.abs().amax(dim=(-1, -2))
-    scale = amax / 127.0 + 1e-7
+    scale = fma_f32(amax, torch.tensor(1.0, dtype=torch.float32) / 127.0, torch.tensor(1e-7, dtype=torch.float32))
     y = x32 / scale.view(B, H, nb, 1, 1)
     y = y + torch.where(y >= 0, 0.5, -0.5).to(torch.float32)
     x_int8 = y.to(torch.int8).view(B, H, nb * bs, D)[:, :, :N].contiguous()
@@ -267,17 +300,25 @@ def predictor(q, k, km, is_causal=False, simthreshd1=-0.1, cdfthreshd=None, topk
 
 
 # ----------------------------------------------------------------------------- V quantisation
-def quant_v(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """spas_sage_attn/core.py:115-117,143-151 + csrc/fused/fused.cu:80-191.
+def quant_v(v: torch.Tensor, recip_scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """spas_sage_attn/core.py:115-117,143-151 + csrc/fused/fused.cu:80-191 (built with --use_fast_math).
 
     v: [B,H,N,D] any float dtype.  Returns (v8 [B,H,N_pad128,D] as e4m3 values in fp32, zero rows
     beyond N; v_scale [B,H,D] fp32).  The reference stores the same numbers transposed to
-    [B,H,D,N_pad] with a 16-token permutation that only serves its mma.sync register layout."""
+    [B,H,D,N_pad] with a 16-token permutation that only serves its mma.sync register layout.
+
+    fused.cu:150 `scale = amax / scale_max` and :163 `recp_scale = scale_max / amax` are approximate
+    quotients (dividend times hardware reciprocal).  The first equals amax * RN(1/2.25) on every fixture
+    value.  For the second pass `recip_scale` [B,H,D] = the device's quotient 2.25 / amax to reproduce the
+    reference bit for bit; without it the correctly rounded reciprocal stands in."""
     B, H, N, D = v.shape
     v16 = v.to(torch.float16).float()
     amax = v16.abs().amax(dim=-2)                                     # [B,H,D]
-    v_scale = amax / V_SCALE_MAX
-    r = torch.full_like(amax, V_SCALE_MAX) / amax                     # tensor / tensor: one IEEE division
+    v_scale = amax * (torch.tensor(1.0, dtype=torch.float32) / V_SCALE_MAX)
+    if recip_scale is None:
+        r = V_SCALE_MAX * (torch.ones_like(amax) / amax)
+    else:
+        r = recip_scale.to(torch.float32).reshape(B, H, D)
     r = torch.where(amax > 0, r, torch.zeros_like(r))                 # all-zero channel: emit zeros, not NaN
     v8 = e4m3_round(v16 * r.unsqueeze(-2))
     npad = (N + 127) // 128 * 128

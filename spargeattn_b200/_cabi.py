@@ -42,6 +42,7 @@ SIGNATURES = {
     "sparge_copy2d_async": (_i, [_p, ctypes.c_size_t, _p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, _p]),
     "sparge_selftest_wait_expiry": (_i, [_p, ctypes.c_uint, ctypes.c_uint, _p]),
     "sparge_attn_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p]),
+    "sparge_div_approx": (_i, [_p, _p, _p, _i, _p]),
     "sparge_tensor_peak": (_i, [_i, _i, _i, _i, _p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double), _p]),
 }
 for _name, (_res, _args) in SIGNATURES.items():

@@ -11,7 +11,10 @@
 //   * the self-similarity uses  sum_ij <a_i, a_j> = || sum_i a_i ||^2  with a_i = fp16(x_i * (1/||x_i||));
 //   * a block with fewer than `BS` rows, or with an all-zero row, is never self-similar
 //     (the reference gets there through a 0/0 NaN, utils.py:194-199);
-//   * scale = max|x| / 127 + 1e-7, q = trunc(x / scale + 0.5 * sign) with the IEEE quotient.
+//   * scale = fma(max|x|, RN(1/127), 1e-7): the compiled reference kernel contracts `max / 127. + 1e-7`
+//     (utils.py:206-207) into one FMA with the reciprocal constant -- checked bit for bit against its output
+//     on a B200; q = trunc(x / scale + 0.5 * sign) with the IEEE quotient (the reference's approximate
+//     quotient gave the same INT8 value for every element compared);
 // The quotient is formed without a per-element division: with r = RN(1/scale), y0 = x*r,
 // e = fma(-scale, y0, x) (exact remainder), y = fma(e, r, y0) is the correctly rounded x/scale.
 #include "common.cuh"
@@ -137,7 +140,7 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
   amax = s_amax[0];
 #pragma unroll
   for (int w = 1; w < NW; w++) amax = fmaxf(amax, s_amax[w]);
-  const float scale = __fadd_rn(__fdiv_rn(amax, 127.0f), 1e-7f);
+  const float scale = __fmaf_rn(amax, 1.0f / 127.0f, 1e-7f);
   const float rs = __fdiv_rn(1.0f, scale);
   if (tid == 0) scale_out[(size_t)bh * nb + blk] = scale;
 

@@ -1,5 +1,9 @@
 // Per-channel FP8 (e4m3) quantisation of V: v16 = fp16(v); amax over tokens per (b,h,d);
 // v_scale = amax / 2.25; v8 = e4m3_rn_satfinite(v16 * (2.25 / amax)).
+// The reference builds this file with --use_fast_math (setup.py:60), so both quotients are the approximate
+// `div.approx.ftz.f32` (dividend times the hardware reciprocal of the divisor). The same instruction is used
+// here: div.approx(amax, 2.25) for the scale (equal to amax * RN(1/2.25) on every value checked) and
+// div.approx(2.25, amax) for the multiplier, which makes scales and FP8 bytes equal to the reference's on the same GPU.
 // Replaces the fp16 cast at spas_sage_attn/core.py:115-117, TransposePadPermuteKernel
 // (csrc/fused/fused.cu:26-77) and MeanScaleKernel (fused.cu:80-191).
 // Output is token-major [B,H,N_pad,D] with zero rows beyond N: the tcgen05 PV MMA takes V as an
@@ -12,6 +16,18 @@ namespace sparge {
 
 constexpr int kVRowsPerCta = 256;
 constexpr float kVScaleMax = 2.25f;   // spas_sage_attn/core.py:151
+
+// a / b as fused.cu computes it under --use_fast_math
+__device__ __forceinline__ float div_approx(float a, float b) {
+  float q;
+  asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(q) : "f"(a), "f"(b));
+  return q;
+}
+
+__global__ void div_approx_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = div_approx(a[i], b[i]);
+}
 
 template <typename T>
 __device__ __forceinline__ float to_f16_value(T v);
@@ -64,7 +80,7 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const T* __restrict__ v, c
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const float a = amax[(size_t)bh * D + cg * 8 + i];
-    r[i] = a > 0.f ? __fdiv_rn(kVScaleMax, a) : 0.f;
+    r[i] = a > 0.f ? div_approx(kVScaleMax, a) : 0.f;
   }
   const T* base = v + (size_t)(bh / H) * sb + (size_t)(bh % H) * sh;
   uint8_t* out = v8 + (size_t)bh * N_pad * D;
@@ -84,7 +100,7 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const T* __restrict__ v, c
 
 __global__ void v_scale_final_kernel(float* __restrict__ v_scale, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) v_scale[i] = __fdiv_rn(v_scale[i], kVScaleMax);
+  if (i < n) v_scale[i] = div_approx(v_scale[i], kVScaleMax);
 }
 
 template <typename T, int D>
@@ -115,6 +131,13 @@ extern "C" int sparge_quant_v_strided(const void* v, uint8_t* v8, float* v_scale
   if (dtype == SPARGE_F16) return D == 64 ? SPARGE_QV(__half, 64) : SPARGE_QV(__half, 128);
   return D == 64 ? SPARGE_QV(__nv_bfloat16, 64) : SPARGE_QV(__nv_bfloat16, 128);
 #undef SPARGE_QV
+}
+
+extern "C" int sparge_div_approx(const float* a, const float* b, float* out, int n, sparge_stream_t stream) {
+  if (!a || !b || !out) return SPARGE_ERR_NULL;
+  if (n <= 0) return SPARGE_ERR_INVALID_ARG;
+  sparge::div_approx_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(a, b, out, n);
+  return sparge::launch_status();
 }
 
 extern "C" int sparge_quant_v(const void* v, uint8_t* v8, float* v_scale, int B, int H, int N, int D, int dtype,

@@ -139,6 +139,15 @@ def quant_v(v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return v8, vs
 
 
+def div_approx(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Elementwise a / b as the GPU's `div.approx.ftz.f32` evaluates it (fp32 CUDA tensors of one shape)."""
+    _need_cuda(a, b)
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.shape == b.shape
+    out = torch.empty_like(a)
+    _cabi.check(_cabi.lib.sparge_div_approx(_ptr(a), _ptr(b), _ptr(out), a.numel(), _stream(a)), "sparge_div_approx")
+    return out
+
+
 def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale, k_scale, v_scale, sm_scale: float,
              is_causal: bool, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
              return_pv_count: bool = False):

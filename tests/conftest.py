@@ -11,3 +11,12 @@ for p in (ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests", "golde
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+
+
+def device_recip_scale(v):
+    """2.25 / amax per (batch, head, channel) of V as the GPU's approximate division returns it: the one input
+    of the oracle's V quantiser that has no CPU definition (see sparge_oracle.quant_v). Returns a CPU tensor."""
+    import torch
+    from spargeattn_b200 import ops
+    amax = v.to(torch.float16).float().abs().amax(dim=-2).cuda()
+    return ops.div_approx(torch.full_like(amax, 2.25), amax).cpu()

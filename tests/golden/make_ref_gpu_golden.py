@@ -8,7 +8,9 @@ Each case runs the reference's own code path of spas_sage2_attn_meansim_topk_cud
 (bf16 and fp16; the Triton CPU interpreter used by make_golden.py cannot do bf16 faithfully) and stores
 what the reference produced: the torch K mean, pooled values and self-similarity flags, INT8 Q/K and
 scales, the block map (with `torch.sort(stable=True)`, ties to the lower index), LUT and counts, the FP8
-bytes of V (un-permuted to token-major) with its scales, and the attention output.  `tie_flips` counts the
+bytes of V (un-permuted to token-major) with its scales, and the attention output.  `recip_scale` is the
+GPU's approximate quotient 2.25 / amax per V channel (evaluated by this library's sparge_div_approx with the
+instruction the reference's fast-math build uses): the one input of the V quantiser that has no CPU definition.  `tie_flips` counts the
 blocks of the map that change when the reference's sort is left unstable.  Inputs are not stored: tests
 regenerate them with `ref_gpu_inputs` from the stored seed and check `input_sum`.
 """
@@ -26,7 +28,7 @@ CASES = [
     ("n200_d128", 1, 2, 200, 128, False, 0.5, 0.2, False, 22),
     ("n640_d64_causal", 1, 2, 640, 64, True, 0.5, 0.2, False, 23),
     ("n1000_d128_sink", 1, 1, 1000, 128, False, 0.3, 0.5, True, 24),
-    ("n2048_d64", 1, 2, 2048, 64, False, 0.5, -0.1, False, 25),
+    ("n2048_d64", 1, 1, 2048, 64, False, 0.5, -0.1, False, 25),
 ]
 
 
@@ -44,6 +46,8 @@ def main(out_dir):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import ref_runner as RR
     RR.load()
+    sys.path.insert(0, ROOT)
+    from spargeattn_b200 import ops
     os.makedirs(out_dir, exist_ok=True)
     dev = torch.device("cuda", 0)
     for name, B, H, N, D, causal, topk, sim1, sink, seed in CASES:
@@ -54,6 +58,8 @@ def main(out_dir):
             pr = RR.predictor(rq, rk, km, causal, sim1, None, topk, sink, stable=True)
             pu = RR.predictor(rq, rk, km, causal, sim1, None, topk, sink, stable=False)
             _, vs, v8_tok = RR.quant_v(rv16)
+            amax = rv16.float().abs().amax(dim=-2)
+            recip = ops.div_approx(torch.full_like(amax, 2.25), amax)
             o = RR.api_topk(qd, kd, vd, stable=True, topk=topk, is_causal=causal, simthreshd1=sim1, attention_sink=sink)
             torch.cuda.synchronize()
             fix = dict(case=(B, H, N, D, causal, topk, sim1, sink, seed), dtype=tag,
@@ -61,7 +67,7 @@ def main(out_dir):
                        km=km.cpu(), pq=pr["pq"].cpu(), pk=pr["pk"].cpu(), sim_q=pr["sim_q"].cpu(), sim_k=pr["sim_k"].cpu(),
                        q_int8=pr["q_int8"].cpu(), q_scale=pr["q_scale"].cpu(), k_int8=pr["k_int8"].cpu(),
                        k_scale=pr["k_scale"].cpu(), map=pr["map"].cpu(), lut=pr["lut"].cpu(), valid=pr["valid"].cpu(),
-                       v8=v8_tok.cpu(), v_scale=vs.cpu(), o=o.cpu(),
+                       v8=v8_tok.cpu(), v_scale=vs.cpu(), recip_scale=recip.cpu(), o=o.cpu(),
                        tie_flips=int((pr["map"] != pu["map"]).sum().item()))
             path = os.path.join(out_dir, f"ref_gpu_{name}_{tag}.pt")
             torch.save(fix, path)

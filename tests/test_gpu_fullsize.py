@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import sparge_oracle as O
+from conftest import device_recip_scale
 
 pytestmark = pytest.mark.gpu
 
@@ -105,7 +106,7 @@ def _oracle_front(q, k, v):
     km = O.k_mean(k)
     pq, sim_q, q8, qs = O.pool_sim_quant(q, None, 128, thr)
     pk, sim_k, k8, ks = O.pool_sim_quant(k, km, 64, thr)
-    v8, vs = O.quant_v(v)
+    v8, vs = O.quant_v(v, device_recip_scale(v))
     return dict(km=km, pq=pq, pk=pk, sim_q=sim_q, sim_k=sim_k, q8=q8, qs=qs, k8=k8, ks=ks, v8=v8, vs=vs, thr=thr)
 
 
@@ -214,7 +215,7 @@ def test_cogvideox_size_block_sparse_api_with_bernoulli_mask(n_cut):
     dummy = torch.zeros(H)
     _, _, q8, qs = O.pool_sim_quant(q, None, 128, dummy, want_pool=False)
     _, _, k8, ks = O.pool_sim_quant(k, km, 64, dummy, want_pool=False)
-    v8, vs = O.quant_v(v)
+    v8, vs = O.quant_v(v, device_recip_scale(v))
     kmg = ops.k_mean(kc)
     _, _, q8g, qsg = ops.pool_sim_quant(qc, None, 128, None)
     _, _, k8g, ksg = ops.pool_sim_quant(kc, kmg, 64, None)

@@ -4,6 +4,7 @@ import pytest
 import torch
 
 import sparge_oracle as O
+from conftest import device_recip_scale
 
 pytestmark = pytest.mark.gpu
 
@@ -78,7 +79,7 @@ def test_quant_v_bit_exact(shape, dtype):
     g = torch.Generator().manual_seed(4)
     v = (torch.randn(B, H, N, D, generator=g) * torch.rand(D, generator=g) * 4).to(dtype)
     v[..., 3] = 0             # all-zero channel: zeros out, not NaN
-    v8_o, vs_o = O.quant_v(v)
+    v8_o, vs_o = O.quant_v(v, device_recip_scale(v))
     v8, vs = ops.quant_v(v.cuda())
     assert torch.equal(vs.cpu(), vs_o)
     assert v8.shape == v8_o.shape
@@ -96,7 +97,7 @@ def test_quant_v_rounding_boundaries():
     v[0, 0, 1:7, :] = ties.view(6, 1).to(torch.float16)
     v[0, 0, 7:13, :] = (ties * (1 + 2.0 ** -10)).view(6, 1).to(torch.float16)
     v[0, 0, 13:19, :] = (ties * (1 - 2.0 ** -11)).view(6, 1).to(torch.float16)
-    v8_o, vs_o = O.quant_v(v)
+    v8_o, vs_o = O.quant_v(v, device_recip_scale(v))
     v8, vs = ops.quant_v(v.cuda())
     assert torch.equal(vs.cpu(), vs_o) and torch.equal(v8.cpu(), O.e4m3_bits(v8_o))
 
