@@ -1,18 +1,26 @@
 // LUT-driven block-sparse attention for sm_100a.
 //   S = Q8 K8^T   : tcgen05.mma kind::i8, operands staged by TMA into 128B/64B-swizzled smem,
-//                   s32 accumulator in tensor memory (TMEM)
-//   online softmax in registers (one thread per query row, no shuffles), P rounded to e4m3 and
-//                   written back into the TMEM columns S came from
-//   O += P8 V8    : tcgen05.mma kind::f8f6f4 with A = P from TMEM, B = V tile (token-major,
+//                   s32 accumulator in tensor memory (TMEM). Two live 64-key blocks are paired into one
+//                   N = 128 step: their K tiles sit next to each other in shared memory, so one
+//                   instruction covers both (an odd last block runs as N = 64).
+//   online softmax in registers, two threads per query row (one per block of the pair; they exchange their
+//                   row maxima through shared memory): one running-maximum update, one output rescale and
+//                   one round of hand-offs per 128 keys; P rounded to e4m3 and stored to a 128B-swizzled
+//                   shared-memory tile
+//   O += P8 V8    : tcgen05.mma kind::f8f6f4, A = P tile (K-major), B = V tiles (token-major,
 //                   MN-major descriptor), f32 accumulator in TMEM
 // Replaces qk_int_sv_f8_block_sparse_attn_kernel (csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:42-755)
 // and its host wrapper (csrc/qattn/qk_int_sv_f8_cuda_sm89.cu:392-585).
 //
-// One CTA per (q-block of 128 rows, head, batch); 6 warps:
-//   warps 0-3  softmax / correction / epilogue (thread t owns query row t = TMEM lane t)
-//   warp  4    TMA producer: walks the delta-encoded LUT and fetches only live K/V blocks
-//   warp  5    MMA issuer (one elected lane) and TMEM owner
-// TMEM columns: [0,64) S0/P0, [64,128) S1/P1, [128,128+D) O  -> 256 columns, two CTAs per SM.
+// One CTA per (q-block of 128 rows, head, batch); 10 warps:
+//   warps 0-7  softmax / correction / epilogue (warps w and w + 4 own query rows 32 (w & 3) ... = TMEM lanes)
+//   warp  8    TMA producer: walks the delta-encoded LUT and fetches only live K/V blocks
+//   warp  9    MMA issuer (one elected lane) and TMEM owner
+// Sixteen softmax warps per SM (two CTAs): four per scheduler, enough to keep the exponential unit fed while
+// other warps wait on a hand-off.
+// TMEM columns: [0,128) S of the current step, [128,128+D) O  -> 256 columns, two CTAs per SM.
+// S is single-buffered: the softmax warps release it as soon as their last tcgen05.ld of the step has
+// landed (half way through the step), and QK^T of the next step runs under the second half's exponentials.
 //
 // Every wait is bounded; on expiry the kernel records a code in *dev_status and unwinds.
 #include <cuda.h>
@@ -32,10 +40,13 @@ constexpr float kFastScaleLimit = 0.0078125f;  // 2^-7: bounds the fast path's p
 
 template <int D>
 struct AttnShape {
-  static constexpr int kStages = (D == 128) ? 5 : 8;
+  static constexpr int kStagesK = (D == 128) ? 2 : 4;   // ring slots, each holding a PAIR of 64-key tiles
+  static constexpr int kStagesV = (D == 128) ? 2 : 4;
   static constexpr int kTileQ = 128 * D;
   static constexpr int kTileKV = 64 * D;
-  static constexpr int kSmemBytes = 1024 + kTileQ + kStages * 2 * kTileKV;
+  static constexpr int kPairKV = 2 * kTileKV;
+  static constexpr int kTileP = 128 * 128;              // 128 rows x 128 keys of e4m3
+  static constexpr int kSmemBytes = 1024 + kTileQ + kTileP + (kStagesK + kStagesV) * kPairKV;
   static constexpr int kTmemCols = 256;
   static constexpr uint32_t kSwizzle = (D == 128) ? kSwizzle128B : kSwizzle64B;
 };
@@ -57,8 +68,103 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint32_t* w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+}
+
+// Row maximum of 32 scores, in log2 units. klim: keys with local index >= klim are masked.
+template <bool MASKED>
+__device__ __forceinline__ float chunk_rowmax(const uint32_t* sr, float c, int klim) {
+  if (!MASKED) {
+    int m0 = (int)sr[0], m1 = (int)sr[8], m2 = (int)sr[16], m3 = (int)sr[24];   // four chains: short latency
+#pragma unroll
+    for (int k = 1; k < 7; k += 2) {
+      m0 = __vimax3_s32(m0, (int)sr[k], (int)sr[k + 1]);
+      m1 = __vimax3_s32(m1, (int)sr[8 + k], (int)sr[8 + k + 1]);
+      m2 = __vimax3_s32(m2, (int)sr[16 + k], (int)sr[16 + k + 1]);
+      m3 = __vimax3_s32(m3, (int)sr[24 + k], (int)sr[24 + k + 1]);
+    }
+    m0 = __vimax3_s32(m0, m1, (int)sr[7]);
+    m2 = __vimax3_s32(m2, m3, (int)sr[15]);
+    const int mx = max(__vimax3_s32(m0, m2, (int)sr[23]), (int)sr[31]);
+    return (__int_as_float(mx + (int)kMagicBits) - kMagic) * c;   // c > 0: max commutes with the scaling
+  } else {
+    int mx = INT_MIN;
+#pragma unroll
+    for (int k = 0; k < 32; k++) mx = (k < klim) ? max(mx, (int)sr[k]) : mx;
+    return (klim > 0) ? __int2float_rn(mx) * c : kMaskValue;
+  }
+}
+
+// P = 2^(S*c - m + 8.807) for 32 scores: row sum in fp32 before the e4m3 rounding
+// (ComputeUnit::kCudaCore, qk_int_sv_f8_cuda_sm89.cuh:773), bytes stored to the row's two 16-byte chunks
+// chunk0, chunk0+1 of the 128B-swizzled P tile. `prow` = shared address of the row, rsw = row & 7.
+template <bool EXACT>
+__device__ __forceinline__ float chunk_exp(const uint32_t* sr, float c, float m, int klim, int one, uint32_t prow,
+                                           int chunk0, int rsw) {
+  uint32_t pr[4];
+  if (!EXACT) {
+    // int32 -> fp32 by adding the bit pattern of 1.5 * 2^23 (exact for |S| < 2^22; here |S| <= 127^2 * 128);
+    // the 2^23 bias is taken out again inside the FMA constant. Packed f32x2 FMA / ADD halve the issue slots.
+    // That constant is rounded at the magnitude of 1.5 * 2^23 * c, so the exponents of this block are off
+    // by a common amount of at most 0.75 * c: blocks whose scale is not small take the exact path.
+    // `one` is a kernel argument equal to 1 that the compiler cannot fold: multiplying by it turns the
+    // int->float bias add into an IMAD, which issues on the FMA pipe instead of the half-rate integer pipe.
+    // (Pre-loading the accumulator with the bias through tcgen05.cp, so that no add is needed at all, was
+    // measured 14 % slower: the sixteen 4 KB copies per step delay QK^T more than 64 IMADs cost. Evaluating
+    // a quarter or half of the exponentials as a polynomial on the FMA pipe was 1.5 - 12 % slower: the loop
+    // is bound by issue slots, and each such element costs four more of them than a MUFU does.)
+    const float off = fmaf(-kMagic, c, kFp8Offset - m);
+    const float2 c2 = make_float2(c, c), o2 = make_float2(off, off);
+    float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 32; k += 4) {
+      float2 a = make_float2(__int_as_float((int)sr[k + 0] * one + (int)kMagicBits),
+                             __int_as_float((int)sr[k + 1] * one + (int)kMagicBits));
+      float2 bb = make_float2(__int_as_float((int)sr[k + 2] * one + (int)kMagicBits),
+                              __int_as_float((int)sr[k + 3] * one + (int)kMagicBits));
+      a = __ffma2_rn(a, c2, o2);
+      bb = __ffma2_rn(bb, c2, o2);
+      a.x = ex2_approx(a.x);
+      a.y = ex2_approx(a.y);
+      bb.x = ex2_approx(bb.x);
+      bb.y = ex2_approx(bb.y);
+      s0 = __fadd2_rn(s0, a);
+      s1 = __fadd2_rn(s1, bb);
+      pr[(k >> 2) & 3] = cvt_e4m3x4(a.x, a.y, bb.x, bb.y);
+      if ((k & 12) == 12) st_shared_v4(prow + (uint32_t)(((chunk0 + (k >> 4)) ^ rsw) << 4), pr);
+    }
+    s0 = __fadd2_rn(s0, s1);
+    return s0.x + s0.y;
+  } else {
+    const float off = kFp8Offset - m;
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; k += 4) {
+      float p0 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 0]), c, off));
+      float p1 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 1]), c, off));
+      float p2 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 2]), c, off));
+      float p3 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 3]), c, off));
+      p0 = (k + 0 < klim) ? p0 : 0.f;
+      p1 = (k + 1 < klim) ? p1 : 0.f;
+      p2 = (k + 2 < klim) ? p2 : 0.f;
+      p3 = (k + 3 < klim) ? p3 : 0.f;
+      sum += (p0 + p1) + (p2 + p3);
+      pr[(k >> 2) & 3] = cvt_e4m3x4(p0, p1, p2, p3);
+      if ((k & 12) == 12) st_shared_v4(prow + (uint32_t)(((chunk0 + (k >> 4)) ^ rsw) << 4), pr);
+    }
+    return sum;
+  }
+}
+
+__device__ __forceinline__ void pair_sync(int id) {   // the two warps that share 32 query rows
+  asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
+
+constexpr int kAttnThreads = 320;
+
 template <int D, bool CAUSAL, bool PV_SKIP, typename OutT>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(kAttnThreads, 2)
 attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
             const __grid_constant__ CUtensorMap tmap_v, OutT* __restrict__ o, const int32_t* __restrict__ lut,
             const int32_t* __restrict__ valid, const float* __restrict__ pvthr, const float* __restrict__ q_scale,
@@ -66,17 +172,21 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
             int nq, int nk, float sm_scale_log2, int one, long long osb, long long osh, long long osn,
             int32_t* __restrict__ pv_count) {
   using Shape = AttnShape<D>;
-  constexpr int STAGES = Shape::kStages;
+  constexpr int SK = Shape::kStagesK, SV = Shape::kStagesV;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sKV = smem + Shape::kTileQ;   // stage s: K at sKV + s*2*kTileKV, V right after it
+  uint8_t* sP = smem + Shape::kTileQ;
+  uint8_t* sK = sP + Shape::kTileP;                  // slot s: sK + s * kPairKV
+  uint8_t* sV = sK + SK * Shape::kPairKV;
 
-  __shared__ uint64_t bar_q, bar_kv_full[STAGES], bar_kv_empty[STAGES], bar_s_full[2], bar_p_ready[2], bar_o_done,
-      bar_delta[2];
+  __shared__ uint64_t bar_q, bar_k_full[SK], bar_k_empty[SK], bar_v_full[SV], bar_v_empty[SV], bar_s_full, bar_s_free,
+      bar_p_ready, bar_o_done, bar_delta[2];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_skip[2];
-  __shared__ float s_delta[2][4];
+  __shared__ float s_delta[2][2][4];   // [step parity][block of the pair][row quarter]
+  __shared__ float s_rmax[2][2][128];  // [step parity][thread of the row pair][row]
+  __shared__ int4 s_meta[8];           // per step (ring of 8): block indices of the pair and their K scales (as bits)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // Query blocks are issued last-first: under a causal mask the late rows hold the most live blocks,
@@ -90,30 +200,35 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     const int rows = min(128, N - qi * 128);
     constexpr int kChunks = D * (int)sizeof(OutT) / 16;
     OutT* obase = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qi * 128 * osn;
-    for (int i = tid; i < rows * kChunks; i += 192)
+    for (int i = tid; i < rows * kChunks; i += kAttnThreads)
       reinterpret_cast<uint4*>(obase + (size_t)(i / kChunks) * osn)[i % kChunks] = make_uint4(0, 0, 0, 0);
     if (pv_count && tid < 4) pv_count[row_id * 4 + tid] = 0;
     return;
   }
+  const int nsteps = (cnt + 1) >> 1;
 
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&s_tmem_base, Shape::kTmemCols);
     tmem_relinquish();
   }
-  if (tid == 128) {
+  if (tid == 256) {
     mbar_init(&bar_q, 1);
 #pragma unroll
-    for (int s = 0; s < STAGES; s++) {
-      mbar_init(&bar_kv_full[s], 1);
-      mbar_init(&bar_kv_empty[s], 1);
+    for (int s = 0; s < SK; s++) {
+      mbar_init(&bar_k_full[s], 1);
+      mbar_init(&bar_k_empty[s], 1);
     }
-    mbar_init(&bar_s_full[0], 1);
-    mbar_init(&bar_s_full[1], 1);
-    mbar_init(&bar_p_ready[0], 4);    // one arrival per softmax warp
-    mbar_init(&bar_p_ready[1], 4);
+#pragma unroll
+    for (int s = 0; s < SV; s++) {
+      mbar_init(&bar_v_full[s], 1);
+      mbar_init(&bar_v_empty[s], 1);
+    }
+    mbar_init(&bar_s_full, 1);
+    mbar_init(&bar_s_free, 8);     // one arrival per softmax warp
+    mbar_init(&bar_p_ready, 8);
     mbar_init(&bar_o_done, 1);
-    mbar_init(&bar_delta[0], 4);
-    mbar_init(&bar_delta[1], 4);
+    mbar_init(&bar_delta[0], 8);
+    mbar_init(&bar_delta[1], 8);
     mbar_fence_init();
     s_skip[0] = 0;
     s_skip[1] = 0;
@@ -125,7 +240,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   const uint32_t tO = tbase + 128;
   const int32_t* lrow = lut + row_id * nk;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
@@ -134,276 +249,310 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       mbar_arrive_expect_tx(&bar_q, Shape::kTileQ);
       tma_load_3d(sQ, &tmap_q, &bar_q, 0, qi * 128, bh);
     }
-    int jbase = 0, issued = 0;
-    int ok = 1;
-    for (int n0 = 0; n0 < cnt && ok; n0 += 32) {
-      const int n = n0 + lane;
-      int incl = (n < cnt) ? lrow[n] : 0;
+    // absolute block index of live entry n (n must not decrease between calls): prefix sums of the delta LUT,
+    // 32 entries at a time, so that no load depends on the previous one
+    const float* ksc = k_scale + (size_t)bh * nk;
+    int win = -32, jabs = 0, jcarry = 0;
+    float ks_lane = 0.f, ks_out = 0.f;      // K scale of this lane's entry / of the entry last returned
+    auto block_of = [&](int n) -> int {
+      if (n >= win + 32) {
+        win = n & ~31;
+        int incl = (win + lane < cnt) ? lrow[win + lane] : 0;
 #pragma unroll
-      for (int ofs = 1; ofs < 32; ofs <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, incl, ofs);
-        if (lane >= ofs) incl += t;
-      }
-      const int jabs = jbase + incl;
-      jbase = __shfl_sync(0xffffffffu, jabs, 31);
-      const int lim = min(32, cnt - n0);
-      for (int kk = 0; kk < lim; kk++) {
-        int j = __shfl_sync(0xffffffffu, jabs, kk);
-        j = max(0, min(j, nk - 1));
-        if (lane == 0) {
-          const int nn = n0 + kk, s = nn % STAGES;
-          if (nn >= STAGES) ok = mbar_wait(&bar_kv_empty[s], ((nn / STAGES) - 1) & 1) ? 1 : 0;
-          if (ok) {
-            uint8_t* dK = sKV + s * 2 * Shape::kTileKV;
-            mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Shape::kTileKV);
-            tma_load_3d(dK, &tmap_k, &bar_kv_full[s], 0, j * 64, bh);
-            tma_load_3d(dK + Shape::kTileKV, &tmap_v, &bar_kv_full[s], 0, j * 64, bh);
-            issued = nn + 1;
-          }
+        for (int ofs = 1; ofs < 32; ofs <<= 1) {
+          const int t = __shfl_up_sync(0xffffffffu, incl, ofs);
+          if (lane >= ofs) incl += t;
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
+        jabs = jcarry + incl;
+        jcarry = __shfl_sync(0xffffffffu, jabs, 31);
+        jabs = max(0, min(jabs, nk - 1));
+        ks_lane = ksc[jabs];
       }
+      ks_out = __shfl_sync(0xffffffffu, ks_lane, n - win);
+      return __shfl_sync(0xffffffffu, jabs, n - win);
+    };
+    int ok = 1, issued_k = 0, issued_v = 0;
+    auto load_pair = [&](const CUtensorMap* map, uint8_t* ring, uint64_t* full, uint64_t* empty, int stages, int s, int ja,
+                         int jb, const int4* meta) {   // lane 0 only
+      const int slot = s % stages;
+      if (s >= stages) ok = mbar_wait(&empty[slot], ((s / stages) - 1) & 1) ? 1 : 0;
+      if (!ok) return;
+      // The step's block indices and K scales are published before its K tiles are requested: the softmax
+      // warps read them once S of that step is complete, which is ordered after the tiles' arrival. The ring
+      // slot was last used eight steps ago; the wait above has just shown that step s - stages has retired.
+      if (meta) s_meta[s & 7] = *meta;
+      uint8_t* dst = ring + slot * Shape::kPairKV;
+      mbar_arrive_expect_tx(&full[slot], (jb >= 0 ? 2 : 1) * Shape::kTileKV);
+      tma_load_3d(dst, map, &full[slot], 0, ja * 64, bh);
+      if (jb >= 0) tma_load_3d(dst + Shape::kTileKV, map, &full[slot], 0, jb * 64, bh);
+    };
+    int ja = block_of(0);
+    float ka = ks_out, kb = 0.f;
+    int jb = -1;
+    if (cnt > 1) {
+      jb = block_of(1);
+      kb = ks_out;
+    }
+    if (lane == 0) {
+      const int4 mt = make_int4(ja, max(jb, 0), __float_as_int(ka), __float_as_int(kb));
+      load_pair(&tmap_k, sK, bar_k_full, bar_k_empty, SK, 0, ja, jb, &mt);
+      issued_k = 1;
+    }
+    for (int s = 0; s < nsteps && ok; s++) {
+      int na = -1, nb = -1;
+      if (s + 1 < nsteps) {
+        na = block_of(2 * s + 2);
+        ka = ks_out;
+        kb = 0.f;
+        if (2 * s + 3 < cnt) {
+          nb = block_of(2 * s + 3);
+          kb = ks_out;
+        }
+      }
+      if (lane == 0) {
+        if (s + 1 < nsteps) {
+          const int4 mt = make_int4(na, max(nb, 0), __float_as_int(ka), __float_as_int(kb));
+          load_pair(&tmap_k, sK, bar_k_full, bar_k_empty, SK, s + 1, na, nb, &mt);
+          if (ok) issued_k = s + 2;
+        }
+        if (ok) {
+          load_pair(&tmap_v, sV, bar_v_full, bar_v_empty, SV, s, ja, jb, nullptr);
+          if (ok) issued_v = s + 1;
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ja = na;
+      jb = nb;
     }
     if (!ok && lane == 0) {
       report(dev_status, SPARGE_DEV_TIMEOUT_PRODUCER);
       // drain our own copies before the CTA's shared memory goes away
-      for (int nn = max(0, issued - STAGES); nn < issued; nn++) mbar_wait(&bar_kv_full[nn % STAGES], (nn / STAGES) & 1);
+      for (int s = max(0, issued_k - SK); s < issued_k; s++) mbar_wait(&bar_k_full[s % SK], (s / SK) & 1);
+      for (int s = max(0, issued_v - SV); s < issued_v; s++) mbar_wait(&bar_v_full[s % SV], (s / SV) & 1);
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc(2, 1, 1, 0, 0, 128, 64);   // s32 += s8 * s8, both K-major
-      constexpr uint32_t idesc_pv = make_idesc(1, 0, 0, 0, 1, 128, D);    // f32 += e4m3 * e4m3, B MN-major
+      constexpr uint32_t idesc_qk2 = make_idesc(2, 1, 1, 0, 0, 128, 128);  // s32 += s8 * s8, both K-major, two blocks
+      constexpr uint32_t idesc_qk1 = make_idesc(2, 1, 1, 0, 0, 128, 64);   // odd last block
+      constexpr uint32_t idesc_pv = make_idesc(1, 0, 0, 0, 1, 128, D);     // f32 += e4m3 * e4m3, B MN-major
       constexpr uint32_t sbo = 8 * D;
       bool ok = mbar_wait(&bar_q, 0);
-      auto issue_pv = [&](int m) {
-        const int b = m & 1, s = m % STAGES;
-        ok = mbar_wait(&bar_p_ready[b], (m >> 1) & 1);
-        if (!ok) return;
-        tc_fence_after();
-        if (!(PV_SKIP && s_skip[b])) {
-          const uint32_t vaddr = smem_u32(sKV + s * 2 * Shape::kTileKV + Shape::kTileKV);
+      // Every operand descriptor is built once: this thread shares its scheduler with four softmax warps,
+      // and each instruction it spends between a hand-off and the MMAs it releases delays the other side.
+      // A descriptor's low field is the address in 16-byte units, so moving to another ring slot is one add.
+      uint64_t qd[D / 32], kd[D / 32], pd[4], vd[4];
 #pragma unroll
-          for (int ks = 0; ks < 2; ks++) {
-            const uint64_t bd = make_smem_desc(vaddr + ks * 32 * D, 64 * D, sbo, Shape::kSwizzle);
-            mma_f8_ts(tO, tbase + b * 64 + ks * 8, bd, idesc_pv, (m > 0 || ks > 0) ? 1u : 0u);
-          }
-        }
-        tc_commit(&bar_kv_empty[s]);
-        tc_commit(&bar_o_done);
+      for (int ks = 0; ks < D / 32; ks++) {
+        qd[ks] = make_smem_desc(smem_u32(sQ) + ks * 32, 16, sbo, Shape::kSwizzle);
+        kd[ks] = make_smem_desc(smem_u32(sK) + ks * 32, 16, sbo, Shape::kSwizzle);
+      }
+#pragma unroll
+      for (int ks = 0; ks < 4; ks++) {
+        pd[ks] = make_smem_desc(smem_u32(sP) + ks * 32, 16, 1024, kSwizzle128B);
+        vd[ks] = make_smem_desc(smem_u32(sV) + ks * 32 * D, 64 * D, sbo, Shape::kSwizzle);
+      }
+      constexpr uint64_t kSlotStep = (uint64_t)(Shape::kPairKV >> 4);
+      auto issue_qk = [&](int s) {   // the caller has waited for the K tiles of step s
+        const int slot = s % SK;
+        tc_fence_after();
+        const uint64_t kofs = (uint64_t)slot * kSlotStep;
+        const uint32_t idesc = (cnt - 2 * s >= 2) ? idesc_qk2 : idesc_qk1;
+#pragma unroll
+        for (int ks = 0; ks < D / 32; ks++) mma_i8_ss(tbase, qd[ks], kd[ks] + kofs, idesc, ks > 0 ? 1u : 0u);
+        tc_commit(&bar_k_empty[slot]);
+        tc_commit(&bar_s_full);
       };
-      for (int n = 0; n < cnt && ok; n++) {
-        const int s = n % STAGES;
-        ok = mbar_wait(&bar_kv_full[s], (n / STAGES) & 1);
+      if (ok) ok = mbar_wait(&bar_k_full[0], 0);
+      if (ok) issue_qk(0);
+      uint32_t o_started = 0;
+      for (int s = 0; s < nsteps && ok; s++) {
+        // Tiles arrive long before the softmax warps' hand-offs: their barriers are checked first, so that
+        // only one wait stands between a hand-off and the MMAs it releases.
+        if (s + 1 < nsteps) {
+          ok = mbar_wait(&bar_k_full[(s + 1) % SK], ((s + 1) / SK) & 1);
+          if (!ok) break;
+          ok = mbar_wait(&bar_s_free, s & 1);      // every softmax warp has read S(s) into registers
+          if (!ok) break;
+          issue_qk(s + 1);
+        }
+        const int slot = s % SV;
+        ok = mbar_wait(&bar_v_full[slot], (s / SV) & 1);
+        if (!ok) break;
+        const uint64_t vofs = (uint64_t)slot * kSlotStep;
+        const int nb = min(2, cnt - 2 * s);
+        ok = mbar_wait(&bar_p_ready, s & 1);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t qaddr = smem_u32(sQ), kaddr = smem_u32(sKV + s * 2 * Shape::kTileKV);
-#pragma unroll
-        for (int ks = 0; ks < D / 32; ks++) {
-          const uint64_t ad = make_smem_desc(qaddr + ks * 32, 16, sbo, Shape::kSwizzle);
-          const uint64_t bd = make_smem_desc(kaddr + ks * 32, 16, sbo, Shape::kSwizzle);
-          mma_i8_ss(tbase + (n & 1) * 64, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
+        if (!(PV_SKIP && s_skip[0])) {
+          mma_f8_ss(tO, pd[0], vd[0] + vofs, idesc_pv, o_started);
+          mma_f8_ss(tO, pd[1], vd[1] + vofs, idesc_pv, 1u);
+          o_started = 1;
         }
-        tc_commit(&bar_s_full[n & 1]);
-        if (n > 0) issue_pv(n - 1);
+        if (nb == 2 && !(PV_SKIP && s_skip[1])) {
+          mma_f8_ss(tO, pd[2], vd[2] + vofs, idesc_pv, o_started);
+          mma_f8_ss(tO, pd[3], vd[3] + vofs, idesc_pv, 1u);
+          o_started = 1;
+        }
+        tc_commit(&bar_v_empty[slot]);
+        tc_commit(&bar_o_done);
       }
-      if (ok) issue_pv(cnt - 1);
       if (!ok) report(dev_status, SPARGE_DEV_TIMEOUT_MMA);
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax / correction / epilogue
-    const uint32_t tlane = (uint32_t)(warp * 32) << 16;
-    const int qrow = qi * 128 + tid;
+    // Two threads per query row (warps w and w + 4 share TMEM lanes 32 * (w & 3) ...): in a two-block step
+    // thread `half` = 0 takes block A (S columns 0..63) and thread 1 block B (64..127); in an odd last step
+    // they split the single block's 64 columns. Each thread works on its columns 32 at a time.
+    const int half = warp >> 2, wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const uint32_t tlane = (uint32_t)(wq * 32) << 16;
+    const uint32_t tS = tbase + tlane;
+    const int qrow = qi * 128 + row;
     const float qs = q_scale[row_id] * sm_scale_log2;
     const float thr = PV_SKIP ? pvthr[h] : 0.f;
-    const float* ksc = k_scale + (size_t)bh * nk;
-    // `one` is a kernel argument equal to 1 that the compiler cannot fold: multiplying by it turns the
-    // int->float bias add into an IMAD, which issues on the FMA pipe instead of the half-rate integer pipe.
+    const uint32_t prow = smem_u32(sP) + (uint32_t)row * 128u;
+    const int rsw = row & 7;
     float m = kMaskValue, d = 0.f;
-    // Software-pipelined metadata: the LUT delta is loaded two iterations ahead and the K scale one
-    // iteration ahead, and neither value is touched before the iteration after its load, so the two
-    // dependent global loads never stall the in-order issue of this warp.
-    int j_cur = max(0, min(lrow[0], nk - 1));
-    float ks_cur = ksc[j_cur];
-    int j_nxt = max(0, min(j_cur + ((cnt > 1) ? lrow[1] : 0), nk - 1));
-    float ks_nxt = ksc[j_nxt];
-    int delta_nn = (cnt > 2) ? lrow[2] : 0;
     bool ok = true;
     int npv = 0;   // PV products issued for this query block (all of them unless the skip test fires)
-    for (int n = 0; n < cnt; n++) {
-      const int j = j_cur;
-      const float c = qs * ks_cur;
-      j_cur = j_nxt;
-      ks_cur = ks_nxt;
-      j_nxt = max(0, min(j_nxt + delta_nn, nk - 1));
-      ks_nxt = ksc[j_nxt];                                 // consumed in iteration n+2
-      delta_nn = (n + 3 < cnt) ? lrow[n + 3] : 0;          // consumed in iteration n+1
-      const int b = n & 1;
-      const uint32_t tS = tbase + b * 64 + tlane;
-      ok = mbar_wait(&bar_s_full[b], (n >> 1) & 1);
+    for (int s = 0; s < nsteps; s++) {
+      const int nb = min(2, cnt - 2 * s);
+      const int col0 = (nb == 2) ? half * 64 : half * 32;      // first S column of this thread
+      const int nch = nb;                                       // 32-column chunks this thread handles
+      ok = __all_sync(0xffffffffu, mbar_wait(&bar_s_full, s & 1));
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[64];
-      tmem_ld32(tS, sr);
-      tmem_ld32(tS + 32, sr + 32);
-      tmem_wait_ld();
+      // this thread's block and scale (published by the producer warp before the step's K tiles were requested)
+      const int4 mt = s_meta[s & 7];
+      const bool second = (nb == 2) && half;
+      const int j = second ? mt.y : mt.x;
+      const float c = qs * __int_as_float(second ? mt.w : mt.z);
+      // per-key mask limit of this row inside the block: keys with block-local index >= klim are masked
       const int key0 = j * 64;
-      const bool masked_block = (key0 + 64 > N) || (CAUSAL && (key0 + 63 > qi * 128));
-      // per-key mask limit for this row: keys with local index >= klim are masked
+      const bool masked = (key0 + 64 > N) || (CAUSAL && (key0 + 63 > qi * 128));
       int klim = 64;
-      if (masked_block) {
+      if (masked) {
         klim = min(64, N - key0);
         if (CAUSAL) klim = min(klim, qrow - key0 + 1);
         klim = max(klim, 0);
       }
-      float rmax;
-      if (!masked_block) {
-        int m0 = (int)sr[0], m1 = (int)sr[16], m2 = (int)sr[32], m3 = (int)sr[48];   // four chains: short latency
-#pragma unroll
-        for (int k = 1; k < 15; k += 2) {
-          m0 = __vimax3_s32(m0, (int)sr[k], (int)sr[k + 1]);
-          m1 = __vimax3_s32(m1, (int)sr[16 + k], (int)sr[16 + k + 1]);
-          m2 = __vimax3_s32(m2, (int)sr[32 + k], (int)sr[32 + k + 1]);
-          m3 = __vimax3_s32(m3, (int)sr[48 + k], (int)sr[48 + k + 1]);
-        }
-        m0 = __vimax3_s32(m0, m1, (int)sr[15]);
-        m2 = __vimax3_s32(m2, m3, (int)sr[31]);
-        const int mx = max(__vimax3_s32(m0, m2, (int)sr[47]), (int)sr[63]);
-        rmax = (__int_as_float(mx + (int)kMagicBits) - kMagic) * c;   // c > 0: max commutes with the scaling
-      } else {
-        int mx = INT_MIN;
-#pragma unroll
-        for (int k = 0; k < 64; k++) mx = (k < klim) ? max(mx, (int)sr[k]) : mx;
-        rmax = (klim > 0) ? __int2float_rn(mx) * c : kMaskValue;
+      const int kofs = col0 & 63;                                // block-local index of this thread's first column
+      uint32_t sr[32];
+      tmem_ld32(tS + col0, sr);
+      tmem_wait_ld();
+      float rmax = masked ? chunk_rowmax<true>(sr, c, klim - kofs) : chunk_rowmax<false>(sr, c, 32);
+      if (nch == 2) {
+        tmem_ld32(tS + col0 + 32, sr);
+        tmem_wait_ld();
+        rmax = fmaxf(rmax, masked ? chunk_rowmax<true>(sr, c, klim - kofs - 32) : chunk_rowmax<false>(sr, c, 32));
       }
-      const float m_new = fmaxf(m, rmax);
-      // PV-skip test (qk_int_sv_f8_cuda_sm89.cuh:317-353): the block is skipped when, over all 128 rows,
-      // max(row maximum - running maximum) + threshold <= 0. The four warps publish their partial maxima
-      // now and read the result only after the exponentials, so the reduction latency is hidden; a block
-      // that turns out to be skipped has wasted its exponentials (rare) but leaves no trace: its row sums
-      // are dropped and the MMA warp does not issue its PV product.
-      const bool skip_candidate = PV_SKIP && n < cnt - 2;   // the last two live blocks are never skipped
-      if (skip_candidate) {
-        const float wmax = warp_max(rmax - m);
+      // exchange the partial row maxima of the two threads of a row
+      s_rmax[s & 1][half][row] = rmax;
+      pair_sync(1 + wq);
+      const float r0 = s_rmax[s & 1][0][row], r1 = s_rmax[s & 1][1][row];
+      const float m1 = fmaxf(m, r0);                              // two-block step: maximum after block A
+      const float m2 = fmaxf(m1, r1);
+      // PV-skip test (qk_int_sv_f8_cuda_sm89.cuh:317-353), per 64-key block as in the reference: block A is
+      // tested against the running maximum before it, block B against the maximum after A. The warps
+      // publish their partial maxima now and read the result only after the exponentials, so the reduction
+      // latency is hidden; the last two live blocks are never skipped.
+      const bool candA = PV_SKIP && (2 * s < cnt - 2), candB = PV_SKIP && (nb == 2) && (2 * s + 1 < cnt - 2);
+      if (PV_SKIP && (candA || candB)) {
+        // half 0 publishes block A's delta, half 1 block B's (a single-block step cannot be a candidate)
+        const float w = warp_max(half ? (r1 - m1) : (r0 - m));
         if (lane == 0) {
-          s_delta[b][warp] = wmax;
-          mbar_arrive(&bar_delta[b]);
+          s_delta[s & 1][half][wq] = w;
+          mbar_arrive(&bar_delta[s & 1]);
         }
       }
-      // Rescaling of the running output is deferred until after the exponentials: by then PV(n-1) has
-      // normally retired, so the wait below does not stall. The wait itself is unconditional: a parity
-      // wait only tells phases apart if every phase of the barrier is observed in order.
-      const float alpha = (n > 0) ? ex2_approx(m - m_new) : 0.f;
-      const bool need_rescale = (n > 0) && __any_sync(0xffffffffu, m_new > m);
-      auto settle_output = [&]() -> bool {
-        if (n > 0) {
-          if (!mbar_wait(&bar_o_done, (n - 1) & 1)) return false;
-          if (need_rescale) {   // some row of this warp raised its maximum
-            tc_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-              uint32_t ov[32];
-              tmem_ld32(tO + tlane + c0, ov);
-              tmem_wait_ld();
-              const float2 al2 = make_float2(alpha, alpha);
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const float2 r2 = __fmul2_rn(make_float2(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1])), al2);
-                ov[i] = __float_as_uint(r2.x);
-                ov[i + 1] = __float_as_uint(r2.y);
-              }
-              tmem_st32(tO + tlane + c0, ov);
-            }
-            tmem_wait_st();
-          }
-        }
-        return true;
-      };
-      d *= alpha;
-      m = m_new;
-      uint32_t pr[16];
-      float sum;
-      if (!masked_block && c < kFastScaleLimit) {
-        // int32 -> fp32 by adding the bit pattern of 1.5 * 2^23 (exact for |S| < 2^22; here |S| <= 127^2 * 128);
-        // the 2^23 bias is taken out again inside the FMA constant. Packed f32x2 FMA / ADD halve the issue slots.
-        // That constant is rounded at the magnitude of 1.5 * 2^23 * c, so the exponents of this block are off
-        // by a common amount of at most 0.75 * c: blocks whose scale is not small take the exact path below.
-        const float off = fmaf(-kMagic, c, kFp8Offset - m);
-        const float2 c2 = make_float2(c, c), o2 = make_float2(off, off);
-        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int k = 0; k < 64; k += 4) {
-          float2 a = make_float2(__int_as_float((int)sr[k + 0] * one + (int)kMagicBits),
-                                 __int_as_float((int)sr[k + 1] * one + (int)kMagicBits));
-          float2 bb = make_float2(__int_as_float((int)sr[k + 2] * one + (int)kMagicBits),
-                                  __int_as_float((int)sr[k + 3] * one + (int)kMagicBits));
-          a = __ffma2_rn(a, c2, o2);
-          bb = __ffma2_rn(bb, c2, o2);
-          a.x = ex2_approx(a.x);
-          a.y = ex2_approx(a.y);
-          bb.x = ex2_approx(bb.x);
-          bb.y = ex2_approx(bb.y);
-          s0 = __fadd2_rn(s0, a);
-          s1 = __fadd2_rn(s1, bb);
-          pr[k >> 2] = cvt_e4m3x4(a.x, a.y, bb.x, bb.y);
-          // P goes to TMEM four words at a time, as soon as they exist, instead of being parked in 16
-          // registers until the end of the block.
-          if ((k & 12) == 12) tmem_st4(tS + (k >> 2) - 3, pr + (k >> 2) - 3);
-        }
-        s0 = __fadd2_rn(s0, s1);
-        sum = s0.x + s0.y;
-      } else {
-        const float off = kFp8Offset - m;
-        sum = 0.f;
-#pragma unroll
-        for (int k = 0; k < 64; k += 4) {
-          float p0 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 0]), c, off));
-          float p1 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 1]), c, off));
-          float p2 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 2]), c, off));
-          float p3 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 3]), c, off));
-          p0 = (k + 0 < klim) ? p0 : 0.f;
-          p1 = (k + 1 < klim) ? p1 : 0.f;
-          p2 = (k + 2 < klim) ? p2 : 0.f;
-          p3 = (k + 3 < klim) ? p3 : 0.f;
-          sum += (p0 + p1) + (p2 + p3);
-          pr[k >> 2] = cvt_e4m3x4(p0, p1, p2, p3);
-        }
-        tmem_st16(tS, pr);
-      }
-      bool skip = false;
-      if (skip_candidate) {
-        ok = mbar_wait(&bar_delta[b], (n >> 1) & 1);
+      const float alpha = (s > 0) ? ex2_approx(m - m2) : 0.f;
+      const bool need_rescale = (s > 0) && __any_sync(0xffffffffu, m2 > m);
+      // PV(s-1) must have retired before P is overwritten and before O is rescaled. (A second P buffer, which
+      // takes this wait off all steps that do not rescale, was measured slower: the kernel is bound by issue
+      // slots and the exponential unit together, not by this hand-off.)
+      if (s > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar_o_done, (s - 1) & 1));
         if (!ok) break;
-        const float dcta = fmaxf(fmaxf(s_delta[b][0], s_delta[b][1]), fmaxf(s_delta[b][2], s_delta[b][3]));
-        skip = (dcta + thr <= 0.f);
+        if (need_rescale) {   // some row of this warp raised its maximum: this thread rescales its half of O
+          tc_fence_after();
+#pragma unroll
+          for (int c0 = 0; c0 < D / 2; c0 += 16) {   // 16 columns at a time: 32 scores are still held in registers
+            uint32_t ov[16];
+            tmem_ld16(tO + tlane + half * (D / 2) + c0, ov);
+            tmem_wait_ld();
+            const float2 al2 = make_float2(alpha, alpha);
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              const float2 r2 = __fmul2_rn(make_float2(__uint_as_float(ov[i]), __uint_as_float(ov[i + 1])), al2);
+              ov[i] = __float_as_uint(r2.x);
+              ov[i + 1] = __float_as_uint(r2.y);
+            }
+            tmem_st16(tO + tlane + half * (D / 2) + c0, ov);
+          }
+          tmem_wait_st();
+        }
       }
-      if (!skip) {
-        d += sum;
-        npv++;
+      d *= alpha;
+      m = m2;
+      const bool exact = masked || !(c < kFastScaleLimit);
+      float sum = 0.f;
+      if (nch == 2) {   // the second 32 columns are still in registers
+        sum = exact ? chunk_exp<true>(sr, c, m, klim - kofs - 32, one, prow, (col0 >> 4) + 2, rsw)
+                    : chunk_exp<false>(sr, c, m, 32, one, prow, (col0 >> 4) + 2, rsw);
+        tmem_ld32(tS + col0, sr);            // the first 32 again: they did not stay in registers
+        tmem_wait_ld();
       }
-      ok = settle_output();
-      if (!ok) break;
-      tmem_wait_st();   // P of a skipped block is stored too; its PV product is simply never issued
-      if (PV_SKIP && tid == 0) s_skip[b] = skip ? 1 : 0;
+      // S has been read for the last time: the MMA warp may overwrite it with the next step's scores
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_p_ready[b]);
+      if (lane == 0) mbar_arrive(&bar_s_free);
+      sum += exact ? chunk_exp<true>(sr, c, m, klim - kofs, one, prow, col0 >> 4, rsw)
+                   : chunk_exp<false>(sr, c, m, 32, one, prow, col0 >> 4, rsw);
+      bool skip = false;
+      if (PV_SKIP && (candA || candB)) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&bar_delta[s & 1], (s >> 1) & 1));
+        if (!ok) break;
+        const float* da = s_delta[s & 1][0];
+        const float* db = s_delta[s & 1][1];
+        const bool skipA = candA && (fmaxf(fmaxf(da[0], da[1]), fmaxf(da[2], da[3])) + thr <= 0.f);
+        const bool skipB = candB && (fmaxf(fmaxf(db[0], db[1]), fmaxf(db[2], db[3])) + thr <= 0.f);
+        skip = half ? skipB : skipA;         // candidates only occur in two-block steps: one block per thread
+        if (tid == 0) {
+          s_skip[0] = skipA ? 1 : 0;
+          s_skip[1] = skipB ? 1 : 0;
+        }
+        npv += (skipA ? 0 : 1) + (skipB ? 0 : 1);
+      } else {
+        if (PV_SKIP && tid == 0) {
+          s_skip[0] = 0;
+          s_skip[1] = 0;
+        }
+        npv += nb;
+      }
+      if (!skip) d += sum;
+      fence_proxy_async_smem();      // P bytes visible to the tensor core's operand fetch
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_p_ready);
     }
-    if (ok) ok = mbar_wait(&bar_o_done, (cnt - 1) & 1);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bar_o_done, (nsteps - 1) & 1));
     if (ok) {
       tc_fence_after();
       // One count per 32-row group, the layout of the reference's PV_Count (qk_int_sv_f8_cuda_sm89.cuh:650-656);
       // the skip decision is taken per block, so the four entries of a block are equal.
-      if (pv_count && lane == 0) pv_count[row_id * 4 + warp] = npv;
-      const float inv = rcp_approx(d);
-      const float* vs = v_scale + (size_t)bh * D;
-      OutT* orow = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qrow * osn;
+      if (pv_count && lane == 0 && half == 0) pv_count[row_id * 4 + wq] = npv;
+      // total row sum = the two threads' partial sums
+      s_rmax[0][half][row] = d;
+      pair_sync(1 + wq);
+      const float inv = rcp_approx(s_rmax[0][0][row] + s_rmax[0][1][row]);
+      const float* vs = v_scale + (size_t)bh * D + half * (D / 2);
+      OutT* orow = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qrow * osn + half * (D / 2);
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < D / 2; c0 += 32) {
         uint32_t ov[32];
-        tmem_ld32(tO + tlane + c0, ov);
+        tmem_ld32(tO + tlane + half * (D / 2) + c0, ov);
         tmem_wait_ld();
         uint32_t w[16];
 #pragma unroll
@@ -425,7 +574,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tbase, Shape::kTmemCols);
+  if (warp == 9) tmem_dealloc(tbase, Shape::kTmemCols);
 }
 
 // ---------------------------------------------------------------------------- host side
@@ -468,7 +617,7 @@ static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return SPARGE_ERR_CUDA;
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   const int nq = (N + 127) / 128, nk = (N + 63) / 64;
-  kern<<<dim3(nq, BH), 192, smem, st>>>(tq, tk, tv, (OutT*)o, lut, valid, pvthr, qs, ks, vs, status, N, H, nq, nk,
+  kern<<<dim3(nq, BH), kAttnThreads, smem, st>>>(tq, tk, tv, (OutT*)o, lut, valid, pvthr, qs, ks, vs, status, N, H, nq, nk,
                                         sm_scale_log2, 1, osb, osh, osn, pv_count);
   return launch_status();
 }
