@@ -3,16 +3,23 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload IDX] [--impl ours|reference]
 
-A step is one full call of `spas_sage2_attn_meansim_topk_cuda(q, k, v, topk)` (predictor, INT8/FP8
-quantisers, block-sparse attention) on one batch of synthetic inputs of the named workload.
-Prints ONE JSON line (rank 0).  Metric: dense-equivalent TOPS = 4*B*H*N^2*D / time (causal: half).
-With N GPUs every rank processes its own copy of the workload's heads (weak scaling, no collective
-on the data path); the value is the sum over ranks divided by the slowest rank's time.
+A step is one full call of `spas_sage2_attn_meansim_topk_cuda(q, k, v, topk)` (K mean, predictor, INT8/FP8
+quantisers, block-sparse attention) on the synthetic inputs of the named workload; default = workload 2
+(Wan2.1-1.3B 480p shape, B=1 H=12 N=32760 D=128 bf16, non-causal, topk 0.5).  Prints ONE JSON line (rank 0).
+Metric: dense-equivalent TOPS = 4*B*H*N^2*D / time (causal: half).
 
-`--impl reference` times the CPU restatement of the reference algorithm (the reference has no CPU
-implementation of its own and its CUDA extension cannot be built here) on the host cores.
+With N GPUs the SAME problem is split (strong scaling): the (batch, head, query-block) cells are cut into N
+contiguous runs of equal cost (`sharding.partition_rows`), every rank generates and processes only the heads
+it touches, no collective on the data path; time = slowest rank, value = whole-problem operations / time.
+From 2 GPUs on, the line also carries `ulysses_cfg4`: workload 4 run sequence-parallel (Ulysses all-to-all).
+
+`--impl reference` times the CPU restatement of the reference algorithm (oracle/) on the host cores, one
+complete head per step; it never imports this library's package.  The compiled reference itself (its CUDA
+kernels built for sm_100, oracle/_ref) is timed on the GPU by a child process and reported under
+`reference_on_this_gpu` of the normal line.
 """
 import argparse
+import importlib.util
 import json
 import os
 import subprocess
@@ -23,10 +30,8 @@ import time
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, ROOT)
 
 METRIC = "dense_equivalent_attention_throughput_topk0.5"
-PVTHRESHD = 50.0
 UNIT = "TOPS"
 NOMINAL_8BIT_TOPS = 4500.0
 
@@ -41,20 +46,18 @@ def parse():
     ap.add_argument("--pvthreshd", type=float, default=50.0, help="PV-skip threshold passed to the API (default 50)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other workloads, comparators and the reference-on-GPU leg")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=2)
-    ap.add_argument("--ulysses-heads-per-step", type=int, default=None,
-                    help="workload 4 on several GPUs: heads per pipelined exchange/compute step")
     ap.add_argument("--quick", action="store_true", help="device-resident arm only (for profiler runs)")
     return ap.parse_args()
 
 
-def workload_shape(w):
-    if w["kind"] == "llm":
-        n = w["N"]
-    else:
-        t, hh, ww = w["grid"]
-        n = t * hh * ww + w.get("text", 0)
-    return w["B"], w["H"], n, w["D"]
+def load_synthetic():
+    """spargeattn_b200/synthetic.py by path: the generators need no CUDA library."""
+    spec = importlib.util.spec_from_file_location("sparge_synthetic", os.path.join(ROOT, "spargeattn_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def dense_equiv_ops(B, H, N, D, causal):
@@ -62,16 +65,11 @@ def dense_equiv_ops(B, H, N, D, causal):
     return ops / 2 if causal else ops
 
 
-def config_dict(idx, w, topk, n_gpus, ulysses=False):
-    B, H, N, D = workload_shape(w)
-    sharding = (f"Ulysses sequence parallel over {n_gpus} GPUs: N/{n_gpus} tokens per rank, exchanged to "
-                f"{H // n_gpus} full-length heads per rank and back ("
-                f"{'pipelined copy-engine peer transfers' if n_gpus == 2 else 'NCCL all-to-all'}; strong scaling)") if ulysses else \
-        f"{n_gpus} x full head set (weak scaling, no collective)"
-    return {"workload": f"cfg{idx}:{w['name']} B={B} H={H} N={N} D={D} bf16 {'causal' if w['causal'] else 'non-causal'} "
-                        f"topk={topk} pvthreshd={PVTHRESHD:g}",
-            "per_gpu_heads": H // n_gpus if ulysses else H, "sharding": sharding,
-            "l2_policy": "inputs larger than L2 (q,k,v = %.0f MB per rank)" % (3 * B * H * N * D * 2 / 1e6)}
+def workload_text(syn, idx, topk, pv):
+    w = syn.WORKLOADS[idx]
+    B, H, N, D = syn.workload_shape(idx)
+    return (f"cfg{idx}:{w['name']} B={B} H={H} N={N} D={D} bf16 {'causal' if w['causal'] else 'non-causal'} "
+            f"topk={topk} pvthreshd={pv:g}")
 
 
 # ------------------------------------------------------------------------------------------ clocks
@@ -115,111 +113,228 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------ CPU arm
-_cpu_inputs = {}
-
-
-def cpu_reference_sample(idx, w, topk, q_blocks):
-    """Times the CPU restatement on one head: full preprocessing + attention on the first `q_blocks`
-    query blocks, and extrapolates linearly in heads x query blocks.  Returns (tops, seconds, note)."""
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import sparge_oracle as O
-    from spargeattn_b200 import synthetic
-    torch.set_num_threads(os.cpu_count())
-    B, H, N, D = workload_shape(w)
-    if idx not in _cpu_inputs:
-        q, k, v = synthetic.workload_qkv(idx, "cpu", heads=1)
-        _cpu_inputs[idx] = (q[:1], k[:1], v[:1])
-    q, k, v = _cpu_inputs[idx]
-    nq = (N + 127) // 128
-    qb = min(q_blocks, nq)
+def cpu_head_step(O, syn, idx, topk, cache):
+    """One complete head of the workload through the CPU restatement: K mean, predictor, quantisers, then
+    fp32 attention on the de-quantised operands under the expanded block mask. Returns seconds."""
+    w = syn.WORKLOADS[idx]
+    _, _, N, D = syn.workload_shape(idx)
+    if idx not in cache:
+        cache[idx] = syn.workload_heads_qkv(idx, [(0, 0)], "cpu")
+    q, k, v = cache[idx]
     t0 = time.perf_counter()
     km = O.k_mean(k)
     pr = O.predictor(q, k, km, w["causal"], -0.1, None, topk, False)
     v8, vs = O.quant_v(v)
-    t1 = time.perf_counter()
-    rows = min(qb * 128, N)
-    O.attention_dense_masked(pr["q_int8"][:, :, :rows], pr["q_scale"][:, :, :qb], pr["k_int8"], pr["k_scale"], v8, vs,
-                             pr["map"][:, :, :qb], D ** -0.5, False, torch.bfloat16, q_chunk=512)
-    t2 = time.perf_counter()
-    full = (t1 - t0) * B * H + (t2 - t1) * B * H * nq / qb
-    tops = dense_equiv_ops(B, H, N, D, w["causal"]) / full / 1e12
-    note = (f"1 of {B * H} heads: full predictor+quantisers ({t1 - t0:.2f}s) + masked fp32 attention on the first {qb} "
-            f"of {nq} query blocks ({t2 - t1:.2f}s); extrapolated linearly to all heads and blocks")
-    return tops, full, (t2 - t0), note
+    O.attention_dense_masked(pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v8, vs, pr["map"], D ** -0.5, False,
+                             torch.bfloat16, q_chunk=512)
+    return time.perf_counter() - t0
 
 
-def run_reference(args, idx, w, topk):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+def cpu_sample_note(syn, idx):
+    B, H, N, D = syn.workload_shape(idx)
+    return (f"one complete head per step (1 of {B * H}: heads are independent, the whole call is {B * H} such steps): "
+            f"K mean + predictor + INT8/FP8 quantisers + fp32 attention on the de-quantised operands under the expanded "
+            f"128x64 block mask; value = that head's dense-equivalent operations / its time")
+
+
+def run_reference(args):
+    """CPU restatement on the host cores, one head per step; nothing of the product is imported."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    vals, sample_s, note = [], 0.0, ""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import sparge_oracle as O
+    syn = load_synthetic()
+    torch.set_num_threads(os.cpu_count())
+    idx = args.workload
+    w = syn.WORKLOADS[idx]
+    topk = args.topk if args.topk is not None else w["topk"]
+    B, H, N, D = syn.workload_shape(idx)
+    cache, secs = {}, []
     for i in range(args.warmup + args.steps):
-        tops, full, sample_s, note = cpu_reference_sample(idx, w, topk, q_blocks=32)
+        t = cpu_head_step(O, syn, idx, topk, cache)
         if i >= args.warmup:
-            vals.append((tops, full))
-    tops = sum(v[0] for v in vals) / len(vals)
-    full = sum(v[1] for v in vals) / len(vals)
+            secs.append(t)
+    per_step = sum(secs) / len(secs)
+    tops = dense_equiv_ops(1, 1, N, D, w["causal"]) / per_step / 1e12
     line = {"impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": full * 1e3, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int8-qk/fp8-pv (emulated in fp32 on CPU)", "data": "synthetic",
-            "config": config_dict(idx, w, topk, args.gpus),
-            "cpu_baseline": {"value": tops, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": note},
+            "config": {"workload": workload_text(syn, idx, topk, args.pvthreshd), "step": "one head (see cpu_baseline.sample)"},
+            "cpu_baseline": {"value": tops, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                             "sample": cpu_sample_note(syn, idx)},
             "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------------------ GPU arm helpers
+def t_gpu(fn, reps, warm=2):
+    """CUDA-event time per call on the current stream (the stream every kernel of this library launches on)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def measured_8bit_peaks(ops):
+    """tcgen05.mma rates of this GPU (operands resident in shared memory, N = 128 as the attention kernel issues)."""
+    i8 = ops.tensor_peak("i8", 128, 2, 40.0)
+    f8 = ops.tensor_peak("f8", 128, 2, 40.0)
+    combined = 2.0 / (1.0 / i8["tops"] + 1.0 / f8["tops"])      # half of the kernel's operations are INT8, half FP8
+    return i8["tops"], f8["tops"], combined
+
+
+def attention_parts(S, core, ops, q, k, v, topk, causal, pvthreshd, reps):
+    """Per-kernel times of one call and the attention kernel's active-block rate."""
+    B, H, N, D = q.shape
+    dev = q.device
+    qc, kc, vc = core._prologue(q, k, v, "HND")
+    thr = core.hyperparameter_check(-0.1, H, dev)
+    tk = core.hyperparameter_check(topk, H, dev)
+    pv = core._pv_threshold_tensor(pvthreshd, H, dev)       # None for the API default (test compiled out)
+    km = ops.k_mean(kc)
+    pq, sq, q8, qs = ops.pool_sim_quant(qc, None, 128, thr)
+    pk, sk, k8, ks = ops.pool_sim_quant(kc, km, 64, thr)
+    lut, valid, _ = ops.select_blocks(pq, pk, sq, sk, tk, None, causal, False, best_first=pv is None)
+    v8, vs = ops.quant_v(vc)
+    nd = B * H * N * D
+    nq, nk = (N + 127) // 128, (N + 63) // 64
+    kern = {}
+    t = t_gpu(lambda: ops.k_mean(kc), reps)
+    kern["k_mean"] = {"ms": t, "GBps": 2 * nd / t / 1e6, "alg_bytes": 2 * nd}
+    t = t_gpu(lambda: ops.pool_sim_quant(qc, None, 128, thr), reps)
+    kern["pool_quant_q"] = {"ms": t, "GBps": 3 * nd / t / 1e6, "alg_bytes": 3 * nd}
+    t = t_gpu(lambda: ops.pool_sim_quant(kc, km, 64, thr), reps)
+    kern["pool_quant_k"] = {"ms": t, "GBps": 3 * nd / t / 1e6, "alg_bytes": 3 * nd}
+    sel_bytes = B * H * (2 * (nq + nk) * D + nq * nk * 4)
+    t = t_gpu(lambda: ops.select_blocks(pq, pk, sq, sk, tk, None, causal, False, best_first=pv is None), reps)
+    kern["select"] = {"ms": t, "GBps": sel_bytes / t / 1e6, "alg_bytes": sel_bytes}
+    t = t_gpu(lambda: ops.quant_v(vc), reps)
+    kern["quant_v"] = {"ms": t, "GBps": 3 * nd / t / 1e6, "alg_bytes": 3 * nd}
+    out = torch.empty_like(qc)
+    t_attn = t_gpu(lambda: ops.attn_fwd(q8, k8, v8, lut, valid, pv, qs, ks, vs, D ** -0.5, False, qc.dtype, out), reps)
+    live = int(valid.sum().item())
+    active_flop = 4.0 * 128 * 64 * D * live
+    kern["attn"] = {"ms": t_attn, "active_TOPS": active_flop / (t_attn * 1e-3) / 1e12, "live_blocks": live,
+                    "density": live / float(B * H * nq * nk), "active_flop": active_flop,
+                    # operand bytes one launch has to move at least once: INT8 Q and K, FP8 V, the LUT rows and the output
+                    "alg_bytes": 2 * nd + B * H * nq * 128 * D + 4 * live + 2 * nd}
+    parts = dict(q8=q8, k8=k8, v8=v8, qs=qs, ks=ks, vs=vs, pv=pv, qc=qc, out=out)
+    return kern, parts
+
+
+def config_row(S, core, ops, syn, idx, topk, pvthreshd, dev, peak8, reps=5):
+    """One workload through the public API on this GPU: call latency, dense-equivalent and active-block rates."""
+    w = syn.WORKLOADS[idx]
+    B, H, N, D = syn.workload_shape(idx)
+    heads = [(b, h) for b in range(B) for h in range(H)]
+    q, k, v = (t.view(B, H, N, D) for t in syn.workload_heads_qkv(idx, heads, dev))
+    api = lambda: S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=topk, is_causal=w["causal"], pvthreshd=pvthreshd)
+    ms = t_gpu(api, reps, warm=3)
+    kern, _ = attention_parts(S, core, ops, q, k, v, topk, w["causal"], pvthreshd, reps)
+    a = kern["attn"]
+    row = {"workload": workload_text(syn, idx, topk, pvthreshd), "api_ms": ms,
+           "dense_equiv_TOPS": dense_equiv_ops(B, H, N, D, w["causal"]) / ms / 1e9, "attn_ms": a["ms"],
+           "active_TOPS": a["active_TOPS"], "frac_of_measured_8bit_peak": a["active_TOPS"] / peak8,
+           "density": a["density"],
+           "preprocess_ms": sum(kern[n]["ms"] for n in ("k_mean", "pool_quant_q", "pool_quant_k", "select", "quant_v"))}
+    if idx == 1:    # the same shape through block_sparse_sage2_attn_cuda with a Bernoulli(0.4) block mask, diagonal forced
+        mask = syn.bernoulli_block_mask(B, H, N, 0.4, 1, dev)
+        t = t_gpu(lambda: S.block_sparse_sage2_attn_cuda(q, k, v, mask_id=mask), reps, warm=3)
+        row["block_sparse_api_ms"] = t
+        row["block_sparse_dense_equiv_TOPS"] = dense_equiv_ops(B, H, N, D, False) / t / 1e9
+        row["block_sparse_density"] = float(mask.float().mean().item())
+    del q, k, v
+    torch.cuda.empty_cache()
+    return row
+
+
+def reference_on_gpu(workloads):
+    """The compiled reference timed by a child process (its modules never share a process with this library)."""
+    script = os.path.join(ROOT, "oracle", "time_reference.py")
+    if not os.path.isdir(os.path.join(ROOT, "oracle", "_ref", "spas_sage_attn")):
+        return {"unavailable": "oracle/_ref is not present (built by oracle/build_ref.py where the reference checkout is)"}
+    try:
+        r = subprocess.run([sys.executable, script, "--workloads", ",".join(str(i) for i in workloads), "--block-sparse",
+                            "--steps", "5"], capture_output=True, text=True, timeout=600)
+        rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+        if not rows:
+            err = r.stderr.strip().splitlines()
+            return {"unavailable": "reference run produced no result: " + (err[-1][:200] if err else "no output")}
+        return {"rows": rows, "how": "child process `python oracle/time_reference.py`, CUDA events, 5 steps after 3 warm-ups"}
+    except Exception as e:   # a broken reference leg must not take the benchmark line with it
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+
+def bind_to_gpu_numa_node(local):
+    """Pin this process (and the pinned host buffers it allocates afterwards) to the CPU cores of the GPU's NUMA node."""
+    try:
+        p = torch.cuda.get_device_properties(local)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = []
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            a, _, b = part.partition("-")
+            cpus += list(range(int(a), int(b or a) + 1))
+        os.sched_setaffinity(0, set(cpus))
+        return node
+    except Exception:
+        return None
+
+
 # ------------------------------------------------------------------------------------------ GPU arm
 def main():
-    global PVTHRESHD
     args = parse()
-    PVTHRESHD = args.pvthreshd
-    from spargeattn_b200 import synthetic
-    idx = args.workload
-    w = synthetic.WORKLOADS[idx]
-    topk = args.topk if args.topk is not None else w["topk"]
     if args.impl == "reference":
-        run_reference(args, idx, w, topk)
+        run_reference(args)
         return
+    # in-switch (NVLS) reductions are not needed by anything here, and a rank that dies while bound to an NVLink
+    # multicast object disturbs its peers' GPUs: keep NCCL on plain peer transfers
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
     import spargeattn_b200 as S
-    from spargeattn_b200 import core, ops
+    from spargeattn_b200 import core, ops, sharding, synthetic as syn
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    B, H, N, D = workload_shape(w)
+    idx = args.workload
+    w = syn.WORKLOADS[idx]
+    topk = args.topk if args.topk is not None else w["topk"]
     causal = w["causal"]
-    # workload 4 on several GPUs: Ulysses sequence parallelism (strong scaling, two all-to-alls per call);
-    # every other case: each rank runs the full head set on its own data (weak scaling, no collective)
-    ulysses = world > 1 and w.get("ulysses", False)
-    calls_per_step = 1
-    gen_seed_shift = 0 if ulysses else rank
-    if w["kind"] == "llm":
-        q, k, v = synthetic.llm_prefill_qkv(B, H, N, D, idx + 100 * gen_seed_shift, dev)
-    else:
-        q, k, v = synthetic.video_qkv(B, H, w["grid"], D, idx + 100 * gen_seed_shift, dev, w.get("text", 0),
-                                      w.get("text_first", True))
-    if ulysses:
-        from spargeattn_b200.sharding import ulysses_attention
-        assert N % world == 0 and H % world == 0
-        n_loc = N // world
-        q, k, v = (t[:, :, rank * n_loc:(rank + 1) * n_loc].contiguous() for t in (q, k, v))
-        if world == 2:      # peer exchange: one attention call per group of heads
-            from spargeattn_b200.sharding import auto_heads_per_step
-            hstep = args.ulysses_heads_per_step or auto_heads_per_step(B, N, H // world, dev)
-            calls_per_step = -(-(H // world) // hstep)
-        api = lambda a, b, c: ulysses_attention(a, b, c, topk=topk, is_causal=causal, pvthreshd=args.pvthreshd,
-                                                heads_per_step=args.ulysses_heads_per_step)
-    else:
+    B, H, N, D = syn.workload_shape(idx)
+    nq = (N + 127) // 128
+
+    # ---- this rank's share: contiguous runs of (batch, head, query block) cells of equal expected cost
+    n_sel = max(1, int(topk * ((N + 63) // 64)))
+    row_cost = [min(n_sel, 2 * (i + 1)) for i in range(nq)] if causal else None
+    units = sharding.partition_rows(B, H, nq, world, row_cost)[rank]
+    heads = [(b, h) for (b, h, _, _) in units]
+    q, k, v = syn.workload_heads_qkv(idx, heads, dev)                  # [1, Hloc, N, D]
+    whole = all(a == 0 and n == nq for (_, _, a, n) in units)
+    ranges = torch.tensor([[a, n] for (_, _, a, n) in units], dtype=torch.int32).view(1, len(units), 2)
+    ranges_dev, ranges_max = ranges.to(dev), int(ranges[..., 1].max())
+    if whole:     # every owned head is complete: the public entry point itself
         api = lambda a, b, c: S.spas_sage2_attn_meansim_topk_cuda(a, b, c, topk=topk, is_causal=causal,
                                                                  pvthreshd=args.pvthreshd)
+    else:
+        api = lambda a, b, c: sharding.attention_units(a, b, c, ranges_dev, ranges_max, topk=topk, is_causal=causal,
+                                                       pvthreshd=args.pvthreshd)
 
     def barrier():
         torch.cuda.synchronize()
@@ -243,32 +358,39 @@ def main():
         return ms / steps
 
     # ---- device-resident arm
-    for _ in range(args.warmup):
-        o = api(q, k, v)
+    for _ in range(max(args.warmup, 3)):
+        api(q, k, v)
     clk = ClockSampler(local)
     clk.__enter__()
     ms_step = timed(lambda: api(q, k, v), args.steps)
     ops.check_device_status(dev)
-    total_ops = dense_equiv_ops(B, H, N, D, causal) * (1 if ulysses else world)
+    total_ops = dense_equiv_ops(B, H, N, D, causal)
     value = total_ops / (ms_step * 1e-3) / 1e12
+    config = {"workload": workload_text(syn, idx, topk, args.pvthreshd),
+              "sharding": (f"strong scaling over {world} GPU(s): (batch, head, query-block) cells cut into {world} contiguous "
+                           f"runs of equal cost, no collective; rank 0 owns {[list(u) for u in units]} as (b, h, first block, blocks)"),
+              "l2_policy": "inputs larger than L2 on every rank (q,k,v = %.0f MB on rank 0; L2 126 MB)" % (3 * q.numel() * 2 / 1e6)}
 
     if args.quick:
         clk.__exit__()
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                              "warmup": args.warmup, "ms_per_step": ms_step, "quick": True,
-                              "config": config_dict(idx, w, topk, world, ulysses)}))
+                              "warmup": args.warmup, "ms_per_step": ms_step, "quick": True, "config": config}))
         if dist is not None:
-            if ulysses:
-                from spargeattn_b200.sharding import close_peer_exchanges
-                close_peer_exchanges()
             dist.destroy_process_group()
         return
 
     # ---- end-to-end arm: pinned host buffers in, host buffer out, copies inside the timed region
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty_like(hq).pin_memory()
-    if ulysses:
+    if whole:
+        # the library's host-buffer front end: head chunks pipelined over upload / compute / download streams
+        from spargeattn_b200.host import spas_sage2_attn_meansim_topk_host
+
+        def e2e_step():
+            spas_sage2_attn_meansim_topk_host(hq, hk, hv, out=ho, device=dev, heads_per_chunk=args.e2e_heads_per_chunk,
+                                              topk=topk, is_causal=causal, pvthreshd=args.pvthreshd)
+    else:
         dq, dk, dv = (torch.empty_like(t) for t in (q, k, v))
 
         def e2e_step():
@@ -276,25 +398,22 @@ def main():
             dk.copy_(hk, non_blocking=True)
             dv.copy_(hv, non_blocking=True)
             ho.copy_(api(dq, dk, dv), non_blocking=True)
-    else:
-        # the library's host-buffer front end: head chunks pipelined over upload / compute / download streams
-        from spargeattn_b200.host import spas_sage2_attn_meansim_topk_host
 
-        def e2e_step():
-            spas_sage2_attn_meansim_topk_host(hq, hk, hv, out=ho, device=dev, heads_per_chunk=args.e2e_heads_per_chunk,
-                                              topk=topk, is_causal=causal, pvthreshd=args.pvthreshd)
-
-    for _ in range(2):
+    for _ in range(3):
         e2e_step()
     e2e_steps = max(3, min(args.steps, 10))
     ms_e2e = timed(e2e_step, e2e_steps)
     clk.__exit__()
     e2e_value = total_ops / (ms_e2e * 1e-3) / 1e12
     in_bytes, out_bytes = 3 * q.numel() * 2, q.numel() * 2
+    if dist is not None:       # bytes of the whole job per step
+        t = torch.tensor([float(in_bytes), float(out_bytes)], device=dev)
+        dist.all_reduce(t)
+        in_bytes, out_bytes = int(t[0].item()), int(t[1].item())
 
-    # ---- per-kernel timings on this rank (CUDA events on the launching stream)
-    kernels, roofline = {}, None
-    if rank == 0 and not ulysses:
+    # ---- per-kernel timings and the roofline of the dominant kernel (rank 0, its own share of the problem)
+    kernels, roofline, extras = {}, None, {}
+    if rank == 0:
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -303,97 +422,140 @@ def main():
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
         peak_src = "measured" if peaks else "fallback"
-        qc, kc, vc = core._prologue(q, k, v, "HND")
-        thr = core.hyperparameter_check(-0.1, H, dev)
-        tk = core.hyperparameter_check(topk, H, dev)
-        pv = core._pv_threshold_tensor(args.pvthreshd, H, dev)   # None for the API default (test compiled out)
         reps = max(5, min(args.steps, 20))
-
-        def t_kernel(fn):
-            for _ in range(2):
-                fn()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            return e0.elapsed_time(e1) / reps
-
-        km = ops.k_mean(kc)
-        pq, sq, q8, qs = ops.pool_sim_quant(qc, None, 128, thr)
-        pk, sk, k8, ks = ops.pool_sim_quant(kc, km, 64, thr)
-        lut, valid, _ = ops.select_blocks(pq, pk, sq, sk, tk, None, causal, False, best_first=pv is None)
-        v8, vs = ops.quant_v(vc)
-        nd = B * H * N * D
-        nq, nk = (N + 127) // 128, (N + 63) // 64
-        t = t_kernel(lambda: ops.k_mean(kc))
-        kernels["k_mean"] = {"ms": t, "GBps": 2 * nd / t / 1e6, "alg_bytes": 2 * nd}
-        t = t_kernel(lambda: ops.pool_sim_quant(qc, None, 128, thr))
-        kernels["pool_quant_q"] = {"ms": t, "GBps": 3 * nd / t / 1e6, "alg_bytes": 3 * nd}
-        t = t_kernel(lambda: ops.pool_sim_quant(kc, km, 64, thr))
-        kernels["pool_quant_k"] = {"ms": t, "GBps": 3 * nd / t / 1e6, "alg_bytes": 3 * nd}
-        sel_bytes = B * H * (2 * (nq + nk) * D + nq * nk * 4)
-        t = t_kernel(lambda: ops.select_blocks(pq, pk, sq, sk, tk, None, causal, False, best_first=pv is None))
-        kernels["select"] = {"ms": t, "GBps": sel_bytes / t / 1e6, "alg_bytes": sel_bytes}
-        t = t_kernel(lambda: ops.quant_v(vc))
-        kernels["quant_v"] = {"ms": t, "GBps": 3 * nd / t / 1e6, "alg_bytes": 3 * nd}
-        out = torch.empty_like(qc)
-        attn = lambda: ops.attn_fwd(q8, k8, v8, lut, valid, pv, qs, ks, vs, D ** -0.5, False, qc.dtype, out)
-        t_attn = t_kernel(attn)
-        live = int(valid.sum().item())
-        active_flop = 4.0 * 128 * 64 * D * live
-        achieved = active_flop / (t_attn * 1e-3) / 1e12
-        peak8 = 2.0 * bf16_peak
-        kernels["attn"] = {"ms": t_attn, "active_TOPS": achieved, "live_blocks": live,
-                           "density": live / float(B * H * nq * nk)}
-        # comparator: the same kernel with every block live = a dense INT8/FP8 attention of this shape
-        ones = torch.ones(B, H, nq, nk, dtype=torch.uint8, device=dev)
-        lut_d, valid_d = ops.mask_to_lut(ones)
-        t_dense = t_kernel(lambda: ops.attn_fwd(q8, k8, v8, lut_d, valid_d, pv, qs, ks, vs, D ** -0.5, False, qc.dtype, out))
-        kernels["attn_dense_mask"] = {"ms": t_dense, "dense_TOPS": dense_equiv_ops(B, H, N, D, False) / (t_dense * 1e-3) / 1e12,
-                                      "sparse_kernel_speedup": t_dense / t_attn}
-        del ones, lut_d, valid_d
+        kernels, parts = attention_parts(S, core, ops, q, k, v, topk, causal, args.pvthreshd, reps)
+        # the peak probe loads the tensor pipe for ~0.1 s and can pull the clocks down for a moment: it runs after
+        # the kernels have been timed, and the other workloads below start with their own warm-up calls
+        i8_peak, f8_peak, peak8 = measured_8bit_peaks(ops)
         for kname in ("k_mean", "pool_quant_q", "pool_quant_k", "select", "quant_v"):
             kernels[kname]["frac_of_hbm_peak"] = kernels[kname]["GBps"] / hbm_peak
-        roofline = {"kernel": "attn_kernel (tcgen05 INT8 QK^T + FP8 PV)", "bound": "tensor", "achieved": achieved,
-                    "peak": peak8, "unit": "TFLOP/s", "frac": achieved / peak8,
-                    "peak_note": f"2 x {peak_src} dense bf16 burst ({bf16_peak} TFLOP/s); 8-bit nominal is "
-                                 f"{NOMINAL_8BIT_TOPS} -> frac_of_nominal {achieved / NOMINAL_8BIT_TOPS:.3f}",
-                    "algorithmic_flop_per_launch": active_flop, "launch_ms": t_attn,
-                    "traffic": ATTN_DRAM_TRAFFIC_BYTES.get(idx), "hbm_peak_GBps": hbm_peak}
+        a = kernels["attn"]
+        roofline = {"kernel": "attn_kernel (tcgen05 INT8 QK^T + FP8 PV)", "bound": "tensor", "achieved": a["active_TOPS"],
+                    "peak": peak8, "unit": "TFLOP/s", "frac": a["active_TOPS"] / peak8,
+                    "peak_note": (f"measured in this run with sparge_tensor_peak (tcgen05.mma M=128 N=128 K=32 from shared "
+                                  f"memory, two issuing CTAs per SM, ~40 ms each): kind::i8 {i8_peak:.0f}, kind::f8f6f4 "
+                                  f"{f8_peak:.0f} TOPS; the kernel does half of its operations in each, so peak = their "
+                                  f"harmonic mean. For context: 2 x {peak_src} dense bf16 burst = {2 * bf16_peak:.0f}, "
+                                  f"vendor nominal {NOMINAL_8BIT_TOPS:.0f} (frac_of_nominal {a['active_TOPS'] / NOMINAL_8BIT_TOPS:.3f})"),
+                    "algorithmic_flop_per_launch": a["active_flop"], "launch_ms": a["ms"],
+                    "traffic": None, "traffic_note": "dram bytes of one launch are in profiles/ (ncu); algorithmic operand bytes: "
+                                                     f"{a['alg_bytes']}", "hbm_peak_GBps": hbm_peak}
+        if world == 1 and not args.no_extras:
+            nk = (N + 63) // 64
+            # comparator 1: the same kernel with every block live = a dense INT8/FP8 attention of this shape
+            ones = torch.ones(1, q.shape[1], nq, nk, dtype=torch.uint8, device=dev)
+            lut_d, valid_d = ops.mask_to_lut(ones)
+            t_dense = t_gpu(lambda: ops.attn_fwd(parts["q8"], parts["k8"], parts["v8"], lut_d, valid_d, parts["pv"], parts["qs"],
+                                                 parts["ks"], parts["vs"], D ** -0.5, False, parts["qc"].dtype, parts["out"]), reps)
+            del ones, lut_d, valid_d
+            # comparator 2 (independent): torch's bf16 scaled_dot_product_attention on the same q, k, v
+            t_sdpa = t_gpu(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=causal), reps)
+            extras["dense_comparators"] = {
+                "own_kernel_all_blocks_live": {"ms": t_dense, "dense_TOPS": total_ops / (t_dense * 1e-3) / 1e12},
+                "torch_sdpa_bf16": {"ms": t_sdpa, "dense_TOPS": total_ops / (t_sdpa * 1e-3) / 1e12},
+                "api_call_vs_own_dense_kernel": t_dense / ms_step, "api_call_vs_torch_sdpa": t_sdpa / ms_step,
+                "attn_kernel_vs_own_dense_kernel": t_dense / a["ms"]}
+            del parts
+            torch.cuda.empty_cache()
+            rows = {}
+            if idx == 2:
+                for tk_, pv_ in ((0.3, 50.0), (0.7, 50.0), (0.5, 5.0)):
+                    rows[f"cfg2_topk{tk_:g}_pv{pv_:g}"] = config_row(S, core, ops, syn, 2, tk_, pv_, dev, peak8)
+            del q, k, v
+            torch.cuda.empty_cache()
+            for j in (0, 1, 3, 4):
+                if j != idx:
+                    rows[f"cfg{j}"] = config_row(S, core, ops, syn, j, syn.WORKLOADS[j]["topk"], 50.0, dev, peak8)
+            extras["configs"] = rows
+            extras["reference_on_this_gpu"] = reference_on_gpu([0, 1, 2, 3, 4])
         ops.check_device_status(dev)
+
+    # ---- workload 4 sequence-parallel (Ulysses) as an extra measurement from 2 GPUs on
+    if world > 1 and not args.no_extras:
+        extras["ulysses_cfg4"] = run_ulysses_cfg4(S, syn, sharding, ops, dist, dev, rank, world)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        tops, full, sample_s, note = cpu_reference_sample(idx, w, topk, q_blocks=1 << 30)
-        cpu_baseline = {"value": tops, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": note,
-                        "sample_seconds": sample_s}
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import sparge_oracle as O
+        torch.set_num_threads(os.cpu_count())
+        cache = {}
+        cpu_head_step(O, syn, idx, topk, cache)                      # warm-up (allocator, thread pool)
+        secs = [cpu_head_step(O, syn, idx, topk, cache) for _ in range(3)]
+        per = sum(secs) / len(secs)
+        cpu_baseline = {"value": dense_equiv_ops(1, 1, N, D, causal) / per / 1e12, "unit": UNIT, "cores": os.cpu_count(),
+                        "kind": "port", "sample": cpu_sample_note(syn, idx) + f"; 3 timed heads, {per:.2f} s each",
+                        "sample_seconds": sum(secs)}
 
     if rank == 0:
+        # kernels of this library launched by one API call: k_mean (2), pool_quant (2), select (1),
+        # quant_v (3), attention (1); counted per timed step of the device-resident arm
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-                "scaling": "strong" if ulysses else "weak",
-                "vs_baseline": None, "dtype": "int8-qk/fp8-pv", "data": "synthetic",
-                "config": config_dict(idx, w, topk, world, ulysses), "clocks": clk.summary(),
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "int8-qk/fp8-pv", "data": "synthetic", "config": config,
+                "clocks": clk.summary(),
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": in_bytes,
-                        "d2h_bytes_per_step": out_bytes},
-                "gpu_launches": GPU_LAUNCHES_PER_STEP * args.steps * calls_per_step, "roofline": roofline, "kernels": kernels,
+                        "d2h_bytes_per_step": out_bytes, "numa_node_bound": numa},
+                "gpu_launches": 9 * args.steps * world, "roofline": roofline, "kernels": kernels,
                 "cpu_baseline": cpu_baseline}
+        line.update(extras)
         print(json.dumps(line))
     if dist is not None:
-        if ulysses:
-            from spargeattn_b200.sharding import close_peer_exchanges
-            close_peer_exchanges()
+        sharding.close_peer_exchanges()
         dist.destroy_process_group()
 
 
-# kernels of this library launched by one API call: k_mean (2), pool_quant (2), select (1),
-# quant_v (3, plus one memset), attention (1)
-GPU_LAUNCHES_PER_STEP = 9
-# dram bytes (read + write) of one attention launch, from the ncu capture summarised under profiles/
-ATTN_DRAM_TRAFFIC_BYTES = {2: 154650112 + 70302464}   # profiles/attn_kernel_cfg2_wan480p.md
+def run_ulysses_cfg4(S, syn, sharding, ops, dist, dev, rank, world):
+    """Workload 4 (B=1 H=24 N=119056 D=128, topk 0.4) sequence-parallel: every rank holds N/G tokens of all heads."""
+    try:
+        idx = 4
+        w = syn.WORKLOADS[idx]
+        B, H, N, D = syn.workload_shape(idx)
+        if N % world or H % world:
+            return {"skipped": f"N={N} or H={H} not divisible by {world}"}
+        n_loc = N // world
+        heads = [(0, h) for h in range(H)]
+        # every rank generates the same per-head tensors and keeps its own token slice (one head at a time: 90 MB)
+        qs, ks, vs = [], [], []
+        for hd in heads:
+            a, b, c = syn.workload_heads_qkv(idx, [hd], dev)
+            qs.append(a[:, :, rank * n_loc:(rank + 1) * n_loc].clone())
+            ks.append(b[:, :, rank * n_loc:(rank + 1) * n_loc].clone())
+            vs.append(c[:, :, rank * n_loc:(rank + 1) * n_loc].clone())
+            del a, b, c
+        q, k, v = (torch.cat(t, 1) for t in (qs, ks, vs))
+        del qs, ks, vs
+        fn = lambda: sharding.ulysses_attention(q, k, v, topk=w["topk"], is_causal=False)
+        for _ in range(3):
+            o = fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = 5
+        e0.record()
+        for _ in range(steps):
+            o = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        # byte equality of head 0 with a single-GPU call: rank 0 gathers head 0's output slices and recomputes it alone
+        parts = [torch.empty_like(o[:, :1]) for _ in range(world)]
+        dist.all_gather(parts, o[:, :1].contiguous())
+        equal = None
+        if rank == 0:
+            a, b, c = syn.workload_heads_qkv(idx, [(0, 0)], dev)
+            ref = S.spas_sage2_attn_meansim_topk_cuda(a, b, c, topk=w["topk"])
+            equal = bool(torch.equal(torch.cat(parts, 2), ref))
+        ops.check_device_status(dev)
+        return {"ms_per_step": ms, "dense_equiv_TOPS": dense_equiv_ops(B, H, N, D, False) / ms / 1e9, "n_gpus": world,
+                "tokens_per_rank": n_loc, "heads_per_rank_inside": H // world, "steps": steps,
+                "head0_bytes_equal_to_single_gpu_call": equal}
+    except Exception as e:
+        return {"failed": f"{type(e).__name__}: {e}"[:300]}
+
 
 if __name__ == "__main__":
     main()

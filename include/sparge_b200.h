@@ -164,6 +164,18 @@ int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_int8, const u
                              int is_causal, float sm_scale, long long o_stride_b, long long o_stride_h,
                              long long o_stride_n, int32_t* pv_count, sparge_stream_t stream);
 
+/* sparge_attn_fwd_pv_count restricted to a range of query blocks per (batch, head): q_block_ranges is int32
+ * [B*H][2] in device memory = (first query block, number of query blocks); only those 128-row blocks of o (and
+ * of pv_count) are written. q_blocks_max >= the largest count (it sizes the launch). q_block_ranges == NULL means
+ * every block. This is the unit of the multi-GPU row sharding: the reference's grid cell (query block, head,
+ * batch) is independent of every other (csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:772-780), so ranks can own
+ * disjoint row ranges of a head; the reference itself has no such entry point. */
+int sparge_attn_fwd_rows(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o, const int32_t* lut,
+                         const int32_t* valid, const float* pvthreshd, const float* q_scale, const float* k_scale,
+                         const float* v_scale, int32_t* dev_status, int B, int H, int N, int D, int out_dtype,
+                         int is_causal, float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
+                         int32_t* pv_count, const int32_t* q_block_ranges, int q_blocks_max, sparge_stream_t stream);
+
 /* Failure-detection self test: launches one warp that waits on a barrier nobody signals, bounded by
  * slices x slice_ns nanoseconds (at most 0.1 s in total), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into
  * *dev_status when the bounded wait gives up -- the same code path that sparge_attn_fwd takes if a

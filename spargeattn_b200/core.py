@@ -31,7 +31,10 @@ def hyperparameter_check(hyper, H, device):
         key = (float(hyper), H, str(device))
         cached = _knob_cache.get(key)
         if cached is None:
-            cached = torch.full((H,), float(hyper), device=device, dtype=torch.float32)
+            # built on the host and copied with a blocking transfer: the cached tensor is complete before any
+            # stream can read it (a fill kernel queued on the stream of the first caller would not be ordered
+            # with later callers on other streams). The first use of a knob value should precede graph capture.
+            cached = torch.full((H,), float(hyper), dtype=torch.float32).to(device)
             if len(_knob_cache) < 256:
                 _knob_cache[key] = cached
         return cached
@@ -136,7 +139,10 @@ def _sparsity(valid_block_num, lut, causal_denominator):
 
 
 def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, topk, pvthreshd, attention_sink,
-                       tensor_layout, return_sparsity, kernel_causal):
+                       tensor_layout, return_sparsity, kernel_causal, q_block_ranges=None, q_blocks_max=0):
+    """The path of spas_sage_attn/core.py:105-169. `q_block_ranges` (int32 [B,H,2]: first 128-row query block, count)
+    makes the attention kernel compute only those rows of each head (the multi-GPU row sharding); everything
+    before the attention kernel still covers the whole head, since every query block needs all keys."""
     q, k, v = _prologue(q, k, v, tensor_layout)
     km = ops.k_mean(k) if smooth_k else None
     headdim = q.size(-1)
@@ -151,7 +157,8 @@ def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthre
         scale = 1.0 / (headdim ** 0.5)
     v_fp8, v_scale = ops.quant_v(v)
     o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale,
-                     kernel_causal, q.dtype, out=_empty_like_layout(q))
+                     kernel_causal, q.dtype, out=_empty_like_layout(q), q_block_ranges=q_block_ranges,
+                     q_blocks_max=q_blocks_max)
     if tensor_layout == 'NHD':
         o = o.transpose(-2, -3)
     if return_sparsity:

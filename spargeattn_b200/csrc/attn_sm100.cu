@@ -170,7 +170,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
             const int32_t* __restrict__ valid, const float* __restrict__ pvthr, const float* __restrict__ q_scale,
             const float* __restrict__ k_scale, const float* __restrict__ v_scale, int32_t* dev_status, int N, int H,
             int nq, int nk, float sm_scale_log2, int one, long long osb, long long osh, long long osn,
-            int32_t* __restrict__ pv_count) {
+            int32_t* __restrict__ pv_count, const int32_t* __restrict__ q_ranges) {
   using Shape = AttnShape<D>;
   constexpr int SK = Shape::kStagesK, SV = Shape::kStagesV;
   extern __shared__ uint8_t smem_raw[];
@@ -191,7 +191,13 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // Query blocks are issued last-first: under a causal mask the late rows hold the most live blocks,
   // and starting the longest rows first keeps the final wave short.
-  const int qi = (int)gridDim.x - 1 - (int)blockIdx.x, bh = blockIdx.y, h = bh % H;
+  // With q_ranges, (batch, head) bh computes only its query blocks [begin, begin + count): the unit of the
+  // multi-GPU row sharding. The grid is sized for the largest count; the other CTAs leave at once.
+  const int bh = blockIdx.y, h = bh % H;
+  const int q_begin = q_ranges ? q_ranges[2 * bh] : 0;
+  const int q_count = q_ranges ? min(q_ranges[2 * bh + 1], nq - q_begin) : (int)gridDim.x;
+  if ((int)blockIdx.x >= q_count) return;
+  const int qi = q_begin + q_count - 1 - (int)blockIdx.x;
   const size_t row_id = (size_t)bh * nq + qi;
   int cnt = valid[row_id];
   cnt = min(cnt, nk);
@@ -610,15 +616,16 @@ template <int D, bool CAUSAL, bool PV_SKIP, typename OutT>
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, const int32_t* lut,
                        const int32_t* valid, const float* pvthr, const float* qs, const float* ks, const float* vs,
                        int32_t* status, int BH, int H, int N, float sm_scale_log2, long long osb, long long osh,
-                       long long osn, int32_t* pv_count, cudaStream_t st) {
+                       long long osn, int32_t* pv_count, const int32_t* q_ranges, int q_blocks_max, cudaStream_t st) {
   auto kern = attn_kernel<D, CAUSAL, PV_SKIP, OutT>;
   constexpr int smem = AttnShape<D>::kSmemBytes;
   // function attributes are per device: set on every call (cheap) rather than caching
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return SPARGE_ERR_CUDA;
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   const int nq = (N + 127) / 128, nk = (N + 63) / 64;
-  kern<<<dim3(nq, BH), kAttnThreads, smem, st>>>(tq, tk, tv, (OutT*)o, lut, valid, pvthr, qs, ks, vs, status, N, H, nq, nk,
-                                        sm_scale_log2, 1, osb, osh, osn, pv_count);
+  const int gx = q_ranges ? min(q_blocks_max, nq) : nq;
+  kern<<<dim3(gx, BH), kAttnThreads, smem, st>>>(tq, tk, tv, (OutT*)o, lut, valid, pvthr, qs, ks, vs, status, N, H, nq, nk,
+                                                 sm_scale_log2, 1, osb, osh, osn, pv_count, q_ranges);
   return launch_status();
 }
 
@@ -645,13 +652,15 @@ extern "C" int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int sli
   return sparge::launch_status();
 }
 
-extern "C" int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
-                                        const int32_t* lut, const int32_t* valid, const float* pvthreshd,
-                                        const float* q_scale, const float* k_scale, const float* v_scale,
-                                        int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
-                                        float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
-                                        int32_t* pv_count, sparge_stream_t stream) {
+extern "C" int sparge_attn_fwd_rows(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
+                                    const int32_t* lut, const int32_t* valid, const float* pvthreshd,
+                                    const float* q_scale, const float* k_scale, const float* v_scale,
+                                    int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
+                                    float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
+                                    int32_t* pv_count, const int32_t* q_block_ranges, int q_blocks_max,
+                                    sparge_stream_t stream) {
   using namespace sparge;
+  if (q_block_ranges && q_blocks_max <= 0) return SPARGE_ERR_INVALID_ARG;
   if (!q_int8 || !k_int8 || !v8 || !o || !lut || !valid || !q_scale || !k_scale || !v_scale) return SPARGE_ERR_NULL;
   if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (out_dtype != SPARGE_F16 && out_dtype != SPARGE_BF16))
     return SPARGE_ERR_INVALID_ARG;
@@ -667,7 +676,7 @@ extern "C" int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_in
   const float sl2 = sm_scale * kLog2e;
   const bool causal = is_causal != 0, skip = pvthreshd != nullptr, bf = out_dtype == SPARGE_BF16;
 #define SPARGE_ATTN(DD, C, S, T) \
-  launch_attn<DD, C, S, T>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, BH, H, N, sl2, o_stride_b, o_stride_h, o_stride_n, pv_count, st)
+  launch_attn<DD, C, S, T>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, BH, H, N, sl2, o_stride_b, o_stride_h, o_stride_n, pv_count, q_block_ranges, q_blocks_max, st)
 #define SPARGE_ATTN_T(DD, C, S) (bf ? SPARGE_ATTN(DD, C, S, __nv_bfloat16) : SPARGE_ATTN(DD, C, S, __half))
 #define SPARGE_ATTN_S(DD, C) (skip ? SPARGE_ATTN_T(DD, C, true) : SPARGE_ATTN_T(DD, C, false))
 #define SPARGE_ATTN_C(DD) (causal ? SPARGE_ATTN_S(DD, true) : SPARGE_ATTN_S(DD, false))
@@ -676,6 +685,16 @@ extern "C" int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_in
 #undef SPARGE_ATTN_S
 #undef SPARGE_ATTN_T
 #undef SPARGE_ATTN
+}
+
+extern "C" int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
+                                        const int32_t* lut, const int32_t* valid, const float* pvthreshd,
+                                        const float* q_scale, const float* k_scale, const float* v_scale,
+                                        int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
+                                        float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
+                                        int32_t* pv_count, sparge_stream_t stream) {
+  return sparge_attn_fwd_rows(q_int8, k_int8, v8, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, B, H, N, D,
+                              out_dtype, is_causal, sm_scale, o_stride_b, o_stride_h, o_stride_n, pv_count, nullptr, 0, stream);
 }
 
 extern "C" int sparge_attn_fwd_strided(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,

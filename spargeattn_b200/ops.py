@@ -53,7 +53,8 @@ def device_status_word(device) -> torch.Tensor:
     """One int32 per device that sparge_attn_fwd writes when a bounded in-kernel wait expires."""
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     if key not in _status_words:
-        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+        # host tensor + blocking copy: the word is zero on the device before any stream can launch a kernel on it
+        _status_words[key] = torch.zeros(1, dtype=torch.int32).to(f"cuda:{key}")
     return _status_words[key]
 
 
@@ -150,21 +151,26 @@ def div_approx(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale, k_scale, v_scale, sm_scale: float,
              is_causal: bool, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
-             return_pv_count: bool = False):
+             return_pv_count: bool = False, q_block_ranges: Optional[torch.Tensor] = None, q_blocks_max: int = 0):
     """Block-sparse attention. With `return_pv_count` also returns int32 [B, H, ceil(N/128)*4]: per 32-row group the
-    number of P.V products computed (the `return_pv_count` diagnostic of csrc/qattn/qk_int_sv_f8_cuda_sm89.cu:526-584)."""
-    _need_cuda(q8, k8, v8, lut, valid, pvthreshd, q_scale, k_scale, v_scale)
+    number of P.V products computed (the `return_pv_count` diagnostic of csrc/qattn/qk_int_sv_f8_cuda_sm89.cu:526-584).
+    `q_block_ranges` (int32 [B, H, 2] on the device: first query block, count) restricts each head to a range of
+    128-row query blocks; the other rows of the output are left untouched. `q_blocks_max` >= the largest count."""
+    _need_cuda(q8, k8, v8, lut, valid, pvthreshd, q_scale, k_scale, v_scale, q_block_ranges)
     B, H, N, D = q8.shape
     if out is None:
         out = torch.empty(B, H, N, D, dtype=out_dtype, device=q8.device)
     _need_strided(out)
     status = device_status_word(q8.device)
     pv_count = torch.empty(B, H, (N + 127) // 128 * 4, dtype=torch.int32, device=q8.device) if return_pv_count else None
-    _cabi.check(_cabi.lib.sparge_attn_fwd_pv_count(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
-                                                   _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale),
-                                                   _ptr(status), B, H, N, D, _dt(out), int(bool(is_causal)),
-                                                   float(sm_scale), out.stride(0), out.stride(1), out.stride(2),
-                                                   _ptr(pv_count), _stream(q8)), "sparge_attn_fwd")
+    if q_block_ranges is not None:
+        assert q_block_ranges.dtype == torch.int32 and q_block_ranges.numel() == 2 * B * H and q_blocks_max > 0
+    _cabi.check(_cabi.lib.sparge_attn_fwd_rows(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
+                                               _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale),
+                                               _ptr(status), B, H, N, D, _dt(out), int(bool(is_causal)),
+                                               float(sm_scale), out.stride(0), out.stride(1), out.stride(2),
+                                               _ptr(pv_count), _ptr(q_block_ranges), int(q_blocks_max), _stream(q8)),
+                "sparge_attn_fwd")
     return (out, pv_count) if return_pv_count else out
 
 

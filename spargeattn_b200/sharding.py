@@ -30,6 +30,83 @@ def partition_heads(costs: Sequence[float], world_size: int) -> List[List[int]]:
     return [sorted(o) for o in owned]
 
 
+def partition_rows(B: int, H: int, nq: int, world_size: int, row_cost: Optional[Sequence[float]] = None):
+    """Row sharding of a [B, H] set of heads over `world_size` ranks with no collective: the (batch, head, query
+    block) cells are laid end to end and cut into `world_size` contiguous runs of equal cost, so a rank owns
+    whole heads plus at most two partial ones, each as a contiguous range of 128-row query blocks
+    (12 heads on 8 ranks: one and a half heads each). Keys and values of a partially owned head are needed by
+    both owners; they prepare them independently.
+
+    row_cost[i]: expected work of query block i (its number of live key blocks); default: equal.
+    Returns, per rank, a list of units (b, h, first_query_block, n_query_blocks); every cell appears once."""
+    cost = [1.0] * nq if row_cost is None else [float(c) for c in row_cost]
+    assert len(cost) == nq and world_size >= 1
+    per_head = sum(cost)
+    total = per_head * B * H
+    units: List[List[tuple]] = [[] for _ in range(world_size)]
+    acc, r = 0.0, 0
+    for bh in range(B * H):
+        start = 0
+        for i in range(nq):
+            # cell (bh, i) goes to the rank in whose share its midpoint falls
+            mid = acc + cost[i] / 2.0
+            owner = min(world_size - 1, int(mid * world_size / total)) if total > 0 else 0
+            if owner != r:
+                if i > start:
+                    units[r].append((bh // H, bh % H, start, i - start))
+                start, r = i, owner
+            acc += cost[i]
+        units[r].append((bh // H, bh % H, start, nq - start))
+    return units
+
+
+def attention_units(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_block_ranges: torch.Tensor,
+                    q_blocks_max: Optional[int] = None, **kwargs) -> torch.Tensor:
+    """spas_sage2_attn_meansim_topk_cuda on the heads a rank touches, computing only each head's owned query
+    blocks. q, k, v: [B, Hloc, N, D] (HND); q_block_ranges: int32 [B, Hloc, 2] = (first block, count), on the
+    device or the host; q_blocks_max: the largest count (pass it with device-resident ranges, otherwise it is
+    read back from them, which synchronises). Rows outside the ranges are not written. kwargs: topk, is_causal,
+    simthreshd1, pvthreshd, attention_sink, scale, smooth_k (as the public function)."""
+    from . import core
+    assert kwargs.get("tensor_layout", "HND") == "HND" and not kwargs.get("return_sparsity", False)
+    ranges = q_block_ranges.to(device=q.device, dtype=torch.int32).contiguous()
+    qmax = int(q_block_ranges[..., 1].max()) if q_blocks_max is None else int(q_blocks_max)
+    return core._meansim_attention(q, k, v, kwargs.get("is_causal", False), kwargs.get("scale"), kwargs.get("smooth_k", True),
+                                   kwargs.get("simthreshd1", -0.1), kwargs.get("cdfthreshd"), kwargs.get("topk", 0.5),
+                                   kwargs.get("pvthreshd", 50), kwargs.get("attention_sink", False), "HND", False,
+                                   bool(kwargs.get("is_causal", False)) and core.SAGE2_TOKEN_LEVEL_CAUSAL,
+                                   q_block_ranges=ranges, q_blocks_max=qmax)
+
+
+class StepMonitor:
+    """Host-side liveness check for multi-rank loops, run between steps (no kernel or collective in flight).
+
+    Before a step every rank announces it in a key-value store (any torch.distributed store: the TCPStore the
+    job was launched with, or one made for the purpose) and then waits, with a limit, until every rank has
+    announced it. A rank that raised, exited or hangs does not announce: the others get a RuntimeError that
+    names it *before* they enqueue a collective that could never complete, and can tear down in order. The
+    reference has no counterpart (it runs single-GPU)."""
+
+    def __init__(self, store, rank: int, world_size: int, timeout_s: float = 30.0, prefix: str = "sparge/step"):
+        self.store, self.rank, self.world, self.timeout, self.prefix = store, rank, world_size, timeout_s, prefix
+
+    def enter(self, step: int) -> None:
+        import time
+        # counters only grow: add() returns the current value without blocking, so a missing peer cannot stall us
+        self.store.add(f"{self.prefix}/{self.rank}", 1)
+        deadline = time.monotonic() + self.timeout
+        want = step + 1
+        missing = list(range(self.world))
+        while missing:
+            missing = [r for r in missing if self.store.add(f"{self.prefix}/{r}", 0) < want]
+            if not missing:
+                return
+            if time.monotonic() > deadline:
+                raise RuntimeError(f"rank(s) {missing} did not reach step {step} within {self.timeout:g} s "
+                                   f"(reported by rank {self.rank}); no collective of that step has been started")
+            time.sleep(0.005)
+
+
 def _a2a(x: torch.Tensor, group) -> torch.Tensor:
     out = torch.empty_like(x)
     dist.all_to_all_single(out, x, group=group)
@@ -196,6 +273,11 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
     CUDA tensors on an NCCL group and "p2p" otherwise."""
     if attention is None:
         from .core import spas_sage2_attn_meansim_topk_cuda as attention
+    # checked before the first collective: an exception later would leave the other ranks waiting in an exchange
+    if kwargs.get("return_sparsity", False):
+        raise ValueError("ulysses_attention returns the output shard only: return_sparsity is not supported")
+    if kwargs.get("tensor_layout", "HND") != "HND":
+        raise ValueError("ulysses_attention exchanges [B, H, N/G, D] shards: tensor_layout must be 'HND'")
     G = dist.get_world_size(group)
     r = dist.get_rank(group)
     B, H, n, D = q.shape
@@ -208,9 +290,9 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attenti
     out = torch.empty_like(q)
     cuda = q.is_cuda
     if exchange == "auto":
-        # Measured on B200 (workload of 119 056 tokens, 24 heads): on 2 GPUs the pipelined peer exchange wins
-        # (31.3 ms against 35.1 for "a2a"); on 8 GPUs, 3 heads per rank leave nothing to pipeline and the plain
-        # all-to-all was the fastest measured (8.89 ms against 9.06 for "peer" and 9.07 for "p2p").
+        # Two ranks hold enough heads each to pipeline the exchange behind the attention of other heads, which
+        # the copy-engine peer transfers do without taking SMs; with more ranks and few heads per rank there is
+        # nothing to pipeline and one all-to-all per tensor has the least overhead.
         if cuda and dist.get_backend(group) == "nccl":
             exchange = "peer" if G == 2 else "a2a"
         else:

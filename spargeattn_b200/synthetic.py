@@ -103,6 +103,35 @@ WORKLOADS = {
 }
 
 
+def workload_heads_qkv(idx: int, heads, device="cpu", dtype=torch.bfloat16):
+    """Inputs of the listed (batch, head) pairs of workload `idx` as [1, len(heads), N, D] tensors. Every head has
+    its own seed, so a rank that owns some heads of a sharded run generates exactly the data another rank (or a
+    single-GPU run) would generate for them."""
+    w = WORKLOADS[idx]
+    qs, ks, vs = [], [], []
+    for (b, h) in heads:
+        seed = 1000003 * (idx + 1) + 1009 * b + h
+        if w["kind"] == "llm":
+            q, k, v = llm_prefill_qkv(1, 1, w["N"], w["D"], seed, device, dtype)
+        else:
+            q, k, v = video_qkv(1, 1, w["grid"], w["D"], seed, device, w.get("text", 0), w.get("text_first", True), dtype)
+        qs.append(q)
+        ks.append(k)
+        vs.append(v)
+    return torch.cat(qs, 1), torch.cat(ks, 1), torch.cat(vs, 1)
+
+
+def workload_shape(idx: int) -> Tuple[int, int, int, int]:
+    """(B, H, N, D) of workload `idx`."""
+    w = WORKLOADS[idx]
+    if w["kind"] == "llm":
+        n = w["N"]
+    else:
+        t, hh, ww = w["grid"]
+        n = t * hh * ww + w.get("text", 0)
+    return w["B"], w["H"], n, w["D"]
+
+
 def workload_qkv(idx: int, device="cpu", heads: Optional[int] = None, dtype=torch.bfloat16):
     """Inputs of workload `idx`; `heads` overrides H (a head shard of the same workload)."""
     w = WORKLOADS[idx]

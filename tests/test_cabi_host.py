@@ -103,3 +103,29 @@ def test_product_does_not_import_the_oracle():
     import pathlib
     for p in pathlib.Path(ROOT, "spargeattn_b200").rglob("*.py"):
         assert "oracle" not in p.read_text().replace("the oracle", ""), p
+
+
+def test_integration_stub_compiles_against_the_header(tmp_path):
+    """The reference-side binding shown in INTEGRATION.md is compiled (syntax and types only) against the real header
+    with a minimal stand-in for torch::Tensor: every call in the document matches the declared signatures."""
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no g++")
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    blocks = re.findall(r"```cpp\n(.*?)```", text, flags=re.S)
+    stub = [b for b in blocks if "sparge_topk_forward" in b]
+    assert len(stub) == 1
+    prelude = """
+#include <cstdint>
+namespace at { enum ScalarType { kHalf, kBFloat16 };
+  struct Tensor { long size(int) const; void* data_ptr() const; template <class T> T* data_ptr() const; ScalarType scalar_type() const; };
+  namespace cuda { struct Stream { void* stream() const; }; Stream getCurrentCUDAStream(); } }
+namespace torch { using Tensor = at::Tensor; }
+"""
+    src = tmp_path / "stub.cpp"
+    src.write_text(prelude + stub[0])
+    r = subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr

@@ -243,3 +243,31 @@ def test_return_pv_count_matches_oracle_skip_count():
     assert (cnt == cnt[..., :1]).all() and (cnt[..., 0] <= valid.int()).all() and (cnt[..., 0] >= valid.int().clamp(max=2)).all()
     gpu_skipped = int(valid.sum()) - int(cnt[..., 0].sum())
     assert skipped > 0 and abs(gpu_skipped - skipped) <= max(1, skipped // 100), (gpu_skipped, skipped)
+
+
+@pytest.mark.parametrize("D,causal", [(128, False), (64, False), (128, True)])
+def test_row_range_units_equal_the_full_call(D, causal):
+    """The multi-GPU row sharding computes a range of query blocks per head: those rows must carry the same bytes
+    as the full call, and rows outside the ranges must not be written."""
+    import spargeattn_b200 as S
+    from spargeattn_b200 import ops
+    from spargeattn_b200.sharding import attention_units, partition_rows
+    B, H, N = 1, 3, 1500
+    q, k, v = (t.cuda() for t in _inputs(B, H, N, D, torch.bfloat16, 31))
+    full = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5, is_causal=causal)
+    nq = (N + 127) // 128
+    got = torch.full_like(full, float("nan"))
+    for units in partition_rows(B, H, nq, 4):                      # what each of four ranks would compute
+        heads = [h for (_, h, _, _) in units]
+        ranges = torch.tensor([[a, n] for (_, _, a, n) in units], dtype=torch.int32).view(1, len(units), 2)
+        o = attention_units(q[:, heads], k[:, heads], v[:, heads], ranges, topk=0.5, is_causal=causal)
+        _status_ok()
+        for i, (_, h, a, n) in enumerate(units):
+            r0, r1 = a * 128, min((a + n) * 128, N)
+            got[0, h, r0:r1] = o[0, i, r0:r1]
+    assert torch.equal(got, full)
+    # rows outside a range stay untouched
+    buf_ranges = torch.tensor([[[2, 3]] * H], dtype=torch.int32)
+    from spargeattn_b200 import core
+    o = attention_units(q, k, v, buf_ranges, topk=0.5, is_causal=causal)
+    assert torch.equal(o[:, :, 256:640], full[:, :, 256:640])
