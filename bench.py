@@ -32,6 +32,8 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
 METRIC = "dense_equivalent_attention_throughput_topk0.5"
+# DRAM bytes (read + write) of one attention launch per workload index, as captured by ncu (see profiles/)
+ATTN_DRAM_TRAFFIC_FROM_PROFILE = {2: 155120896 + 69793536}
 UNIT = "TOPS"
 NOMINAL_8BIT_TOPS = 4500.0
 
@@ -438,8 +440,11 @@ def main():
                                   f"harmonic mean. For context: 2 x {peak_src} dense bf16 burst = {2 * bf16_peak:.0f}, "
                                   f"vendor nominal {NOMINAL_8BIT_TOPS:.0f} (frac_of_nominal {a['active_TOPS'] / NOMINAL_8BIT_TOPS:.3f})"),
                     "algorithmic_flop_per_launch": a["active_flop"], "launch_ms": a["ms"],
-                    "traffic": None, "traffic_note": "dram bytes of one launch are in profiles/ (ncu); algorithmic operand bytes: "
-                                                     f"{a['alg_bytes']}", "hbm_peak_GBps": hbm_peak}
+                    "traffic": ATTN_DRAM_TRAFFIC_FROM_PROFILE.get(idx) if world == 1 else None,
+                    "traffic_note": ("dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from the ncu "
+                                     "capture summarised in profiles/attn_kernel_cfg2_wan480p.md (a recorded figure, not measured "
+                                     f"by this run); algorithmic operand bytes of this launch: {a['alg_bytes']}"),
+                    "hbm_peak_GBps": hbm_peak}
         if world == 1 and not args.no_extras:
             nk = (N + 63) // 64
             # comparator 1: the same kernel with every block live = a dense INT8/FP8 attention of this shape

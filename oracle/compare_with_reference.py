@@ -112,6 +112,8 @@ def compare(q, k, v, is_causal=False, topk=0.5, simthreshd1=-0.1, attention_sink
     rep["map_neq"] = _neq(fmap.bool(), rp["map"])
     rep["map_rows_neq"] = int((fmap.bool() != rp["map"]).any(-1).sum())
     rep["valid_neq"] = _neq(valid, rp["valid"])
+    dv = (valid.long() - rp["valid"].long()).abs()
+    rep["valid_absdiff_max"], rep["valid_absdiff_mean"] = int(dv.max()), float(dv.float().mean())
     rep["lut_neq"] = _neq(lut, rp["lut"])
     rep["live_blocks"] = int(rp["valid"].sum())
     # this library's selection kernel fed the reference's own pooled values and flags: isolates the selection rule
@@ -203,6 +205,12 @@ def main():
                 r["case"] = "cfg2-pv5"
                 report["cases"].append(r)
                 print(json.dumps(r), flush=True)
+                # cdf mode on long rows (nk = 512): the reference's cumsum runs in the 16-bit type on the device
+                for cdf_thr in (0.9, 0.98):
+                    r = compare(qq, kk, vv, is_causal=False, topk=None, cdfthreshd=cdf_thr, simthreshd1=-0.1)
+                    r["case"] = f"cfg2-cdf{cdf_thr}"
+                    report["cases"].append(r)
+                    print(json.dumps(r), flush=True)
         del q, k, v
         torch.cuda.empty_cache()
         if a.time:

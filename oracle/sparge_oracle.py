@@ -33,7 +33,9 @@ bit for bit:
     in about 2 of 10^4 FP8 bytes);
   * the pooled score is an fp32 FMA chain over ascending channel index;
   * the row softmax is evaluated in fp64, rounded to fp32, then to the 16-bit dtype;
-  * top-k uses a stable descending order (ties -> lower block index).
+  * top-k uses a stable descending order (ties -> lower block index);
+  * the cdf mode's cumulative sum is the one torch computes on a CUDA device in the 16-bit type
+    (aten_device_cumsum), and its count the upper-bound search torch runs (searchsorted_right).
 
 Reference files are cited as path:line relative to the reference project root.
 """
@@ -238,11 +240,13 @@ def select_blocks(p: torch.Tensor, sim_q: torch.Tensor, sim_k: torch.Tensor, top
     B, H, nq, nk = p.shape
     order = torch.sort(p.float(), dim=-1, descending=True, stable=True)
     if cdfthreshd is not None:
-        # utils.py:398-403: cumulative sum of the sorted probabilities, kept in the 16-bit dtype.
-        # Pinned: the running sum is exact (fp64), rounded to fp32 and then to the 16-bit dtype per element.
-        cdf = torch.cumsum(order.values.double(), dim=-1).float().to(p.dtype).float()
-        thr = cdfthreshd.view(1, H, 1, 1).expand(B, H, nq, 1).contiguous()
-        n_sel = torch.searchsorted(cdf, thr, right=True).squeeze(-1)
+        # utils.py:398-403: torch.cumsum of the sorted probabilities in the 16-bit dtype, then
+        # torch.searchsorted(cdf, threshold, right=True). The reference runs on a CUDA device, where cumsum is
+        # ATen's chunked Sklansky scan with every combine rounded to the 16-bit type (aten_device_cumsum): its
+        # rounding decides the count on long rows, so that scan is restated here, not a mathematically exact sum.
+        cdf = aten_device_cumsum(order.values.to(p.dtype).reshape(B * H * nq, nk)).float()
+        thr = cdfthreshd.to(torch.float32).view(1, H, 1).expand(B, H, nq).reshape(-1)
+        n_sel = searchsorted_right(cdf, thr).view(B, H, nq)
     else:
         n_sel = (topk.to(torch.float32) * nk).to(torch.int64).view(1, H, 1).expand(B, H, nq)
     n_sel = n_sel.clamp(min=1, max=nk)                                # utils.py:289 (>= 1)
@@ -258,6 +262,64 @@ def select_blocks(p: torch.Tensor, sim_q: torch.Tensor, sim_k: torch.Tensor, top
         fmap = fmap.clone()
         fmap[..., 0] = True
     return fmap
+
+
+def aten_scan_log_threads_x(num_rows: int, row_size: int) -> int:
+    """get_log_num_threads_x_inner_scan of ATen/native/cuda/ScanUtils.cuh (torch 2.11), in its uint32 arithmetic."""
+    lx = 0
+    while (1 << lx) < row_size:
+        lx += 1
+    ly = 0
+    while (1 << ly) < num_rows:
+        ly += 1
+    v = ((9 + ((lx - ly) & 0xFFFFFFFF)) & 0xFFFFFFFF) // 2
+    return min(max(4, v), 9)
+
+
+def aten_device_cumsum(x: torch.Tensor) -> torch.Tensor:
+    """torch.cumsum(x, -1) of a contiguous [rows, n] fp16/bf16 matrix as ATen computes it on a CUDA device
+    (tensor_kernel_scan_innermost_dim with std::plus<scalar_t>, ATen/native/cuda/ScanUtils.cuh): the row is cut
+    into chunks of 2 * nx values (nx from aten_scan_log_threads_x); the total of the previous chunks is added to
+    the first value of a chunk; log2(nx) + 1 Sklansky steps combine the chunk, and every addition is rounded to
+    the 16-bit type. Checked bit for bit against recorded device results (tests/golden/ref_gpu_cdf_*.pt)."""
+    R, n = x.shape
+    dt = x.dtype
+    lg = aten_scan_log_threads_x(R, n)
+    nx = 1 << lg
+    W = 2 * nx
+    out = torch.empty_like(x)
+    total = torch.zeros(R, dtype=dt)
+    t = torch.arange(nx)
+    for c0 in range(0, n, W):
+        w = min(W, n - c0)
+        buf = torch.zeros(R, W, dtype=dt)
+        buf[:, :w] = x[:, c0:c0 + w]
+        buf[:, 0] = (buf[:, 0].float() + total.float()).to(dt)
+        for m in range(lg + 1):
+            s = 1 << m
+            a = ((t >> m) << (m + 1)) | s
+            ti, si = a + (t % s), a - 1
+            buf[:, ti] = (buf[:, ti].float() + buf[:, si].float()).to(dt)
+        out[:, c0:c0 + w] = buf[:, :w]
+        total = buf[:, W - 1].clone()
+    return out
+
+
+def searchsorted_right(cdf: torch.Tensor, thr: torch.Tensor) -> torch.Tensor:
+    """torch.searchsorted(cdf, thr, right=True) per row as the upper-bound binary search torch runs (cdf [rows, n]
+    fp32 values, thr [rows] fp32). Written out because a rounded cumulative sum need not be monotone, and then the
+    result is whatever that particular search visits."""
+    R, n = cdf.shape
+    start = torch.zeros(R, dtype=torch.long)
+    end = torch.full((R,), n, dtype=torch.long)
+    rows = torch.arange(R)
+    while bool((start < end).any()):
+        act = start < end
+        mid = start + ((end - start) >> 1)
+        go = ~(cdf[rows, mid.clamp(max=n - 1)] > thr)
+        start = torch.where(act & go, mid + 1, start)
+        end = torch.where(act & ~go, mid, end)
+    return start
 
 
 def block_map_to_lut(block_map: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:

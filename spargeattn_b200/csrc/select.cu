@@ -9,8 +9,15 @@
 //   p      = T( float( exp(double(score) - max) / sum ) )           (fp64 softmax)
 //   top-k  = first n_sel of a stable descending order of p (ties -> lower block index),
 //            n_sel = clamp(int(topk[h] * nk), 1, nk)
-//   cdf    = n_sel = #{ r : T(float(prefix_r)) <= cdfthreshd[h] } over that order, prefix_r the exact
-//            (fp64) running sum of the sorted probabilities, clamped to [1, nk]
+//   cdf    = the reference runs torch.cumsum on the sorted probabilities in the 16-bit type and takes
+//            torch.searchsorted(cdf, cdfthreshd[h], right=True) (utils.py:398-403). On the device that
+//            cumsum is ATen's chunked Sklansky scan (ATen/native/cuda/ScanUtils.cuh,
+//            tensor_kernel_scan_innermost_dim: chunks of 2 * num_threads_x values, every combine rounded to
+//            the 16-bit type, num_threads_x derived from the row count and row length), and its rounding
+//            decides the count on long rows (a bf16 running sum stops growing once the terms fall below
+//            half an ulp). The kernel runs the same scan in the same order and the same binary search with
+//            the fp32 comparison torch uses, so n_sel equals the reference's wherever the 16-bit
+//            probabilities themselves agree; clamped to [1, nk].
 #include <cfloat>
 
 #include "common.cuh"
@@ -73,8 +80,24 @@ __device__ __forceinline__ float key_value<__nv_bfloat16>(uint32_t k) {
 // evaluated twice (once for the sum, once for the probabilities) instead of being stored: at long
 // sequences shared memory per row, not arithmetic, limits how many rows an SM can hold.
 constexpr int kSelRowsPerCta = 4;
-__host__ __device__ inline size_t select_row_bytes(int nk, int D) {
-  return (((size_t)nk * 4 + (size_t)D * 4 + (size_t)nk * 2) + 15) / 16 * 16;
+__host__ __device__ inline int next_pow2(int n) {
+  int p = 1;
+  while (p < n) p <<= 1;
+  return p;
+}
+// log2 of the x-extent of ATen's inner-dimension scan launch (get_log_num_threads_x_inner_scan, uint32 arithmetic)
+__host__ __device__ inline int aten_scan_log_threads_x(uint32_t num_rows, uint32_t row_size) {
+  uint32_t lx = 0, ly = 0;
+  while ((1u << lx) < row_size) ++lx;
+  while ((1u << ly) < num_rows) ++ly;
+  const uint32_t diff = lx - ly;
+  uint32_t v = (9u + diff) / 2u;
+  v = v < 4u ? 4u : v;
+  return (int)(v > 9u ? 9u : v);
+}
+// per-row shared memory: sort / index / score words [next_pow2(nk)] | q [D] floats | keys [nk] | cdf [cdf_len] 16-bit
+__host__ __device__ inline size_t select_row_bytes(int nk, int D, int cdf_len) {
+  return (((size_t)next_pow2(nk) * 4 + (size_t)D * 4 + (size_t)nk * 2 + (size_t)cdf_len * 2) + 15) / 16 * 16;
 }
 
 __device__ __forceinline__ int warp_sum_int(int x) {
@@ -88,19 +111,22 @@ __global__ void __launch_bounds__(kSelRowsPerCta * 32)
 select_kernel(const T* __restrict__ pq, const T* __restrict__ pk, const uint8_t* __restrict__ sim_q,
               const uint8_t* __restrict__ sim_k, const float* __restrict__ topk, const float* __restrict__ cdfthr,
               uint8_t* __restrict__ mask, int32_t* __restrict__ lut, int32_t* __restrict__ valid, int H, int nq, int nk,
-              int is_causal, int sink, int rows_per_cta, int best_first) {
+              int is_causal, int sink, int rows_per_cta, int best_first, int scan_log_nx, int cdf_len) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int qi = blockIdx.x * rows_per_cta + warp, bh = blockIdx.y, h = bh % H;
   const bool active = warp < rows_per_cta && qi < nq;       // inactive warps still help to stage K tiles
   constexpr int kTileRowBytes = D * (int)sizeof(T) + 16;   // 16-byte pad: conflict-free 128-bit reads, one row per lane
   unsigned char* s_tile = smem_raw;
-  const size_t row_bytes = select_row_bytes(nk, D);
+  const size_t row_bytes = select_row_bytes(nk, D, cdf_len);
+  const int P2 = next_pow2(nk);
   unsigned char* base = smem_raw + 32 * kTileRowBytes + (size_t)(active ? warp : 0) * row_bytes;
   int* s_idx = reinterpret_cast<int*>(base);
   float* s_s = reinterpret_cast<float*>(s_idx);            // scores share storage with the index list
-  float* s_q = reinterpret_cast<float*>(s_idx + nk);
+  uint32_t* s_sort = reinterpret_cast<uint32_t*>(s_idx);   // ... and with the sort keys of the cdf mode
+  float* s_q = reinterpret_cast<float*>(s_idx + P2);
   uint16_t* s_key = reinterpret_cast<uint16_t*>(s_q + D);
+  uint16_t* s_cdf = s_key + nk;
   const int k_limit = is_causal ? min(nk, (qi + 1) * (kBlockQ / kBlockK)) : nk;   // causal: k < (q+1)*2
 
   if (active)
@@ -165,55 +191,60 @@ select_kernel(const T* __restrict__ pq, const T* __restrict__ pk, const uint8_t*
   if (cdfthr == nullptr) {
     n_sel = (int)__fmul_rn(topk[h], (float)nk);            // top-k mode: same count for every row of a head
   } else {
-    // cdf mode: n_sel = #{ r : T(prefix_r) <= thr } over the descending order, prefix exact (fp64).
-    // Step 1: smallest key kappa such that the whole set {key >= kappa} stays within the threshold
-    // (16-step bisection; the set sum is monotone in kappa).
+    // cdf mode. Step 1: the stable descending order (ties -> lower block index) as an explicit sequence: a
+    // bitonic sort of (probability bits << 16 | 0xFFFF - index) in shared memory by this warp.
     const float thr = cdfthr[h];
-    uint32_t lo = 0x10000u;                                // invariant: {key >= lo} fits (empty set at 0x10000)
-    {
-      uint32_t cand_hi = 0x10000u, cand_lo = 0u;           // search kappa in [0, 0x10000]
-      while (cand_lo < cand_hi) {
-        const uint32_t mid = (cand_lo + cand_hi) >> 1;
-        double sum = 0.0;
-        for (int j = lane; j < nk; j += 32) {
-          const uint32_t key = s_key[j];
-          if (key >= mid) sum += (double)key_value<T>(key);
+    for (int i = lane; i < P2; i += 32) s_sort[i] = (i < nk) ? (((uint32_t)s_key[i] << 16) | (uint32_t)(0xFFFF - i)) : 0u;
+    __syncwarp();
+    for (int kk = 2; kk <= P2; kk <<= 1) {
+      for (int jj = kk >> 1; jj > 0; jj >>= 1) {
+        for (int i = lane; i < P2; i += 32) {
+          const int ixj = i ^ jj;
+          if (ixj > i) {
+            const uint32_t a = s_sort[i], b = s_sort[ixj];
+            const bool first_larger = (i & kk) == 0;
+            if (first_larger ? (a < b) : (a > b)) {
+              s_sort[i] = b;
+              s_sort[ixj] = a;
+            }
+          }
         }
-        sum = warp_sum(sum);
-        const bool fits = Elem<T>::to_float(Elem<T>::from_float((float)sum)) <= thr;
-        if (fits) cand_hi = mid; else cand_lo = mid + 1;
+        __syncwarp();
       }
-      lo = cand_lo;
     }
-    int cnt_full = 0;
-    double sum_full = 0.0;
-    uint32_t next_key = 0;                                 // largest key below lo
-    bool has_next = false;
-    for (int j = lane; j < nk; j += 32) {
-      const uint32_t key = s_key[j];
-      if (key >= lo) { cnt_full++; sum_full += (double)key_value<T>(key); }
-      else { next_key = max(next_key, key); has_next = true; }
-    }
-    cnt_full = warp_sum_int(cnt_full);
-    sum_full = warp_sum(sum_full);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) next_key = max(next_key, __shfl_xor_sync(0xffffffffu, next_key, o));
-    has_next = __any_sync(0xffffffffu, has_next);
-    n_sel = cnt_full;
-    if (has_next) {
-      // Step 2: part of the next run of equal keys may still fit: largest t with T(sum_full + t*v) <= thr.
-      int run = 0;
-      for (int j = lane; j < nk; j += 32) run += (s_key[j] == next_key);
-      run = warp_sum_int(run);
-      const double v = (double)key_value<T>(next_key);
-      int t_lo = 0, t_hi = run;                            // answer in [0, run]; t = run cannot fit by construction
-      while (t_lo < t_hi) {
-        const int t = (t_lo + t_hi + 1) >> 1;
-        const bool fits = Elem<T>::to_float(Elem<T>::from_float((float)(sum_full + (double)t * v))) <= thr;
-        if (fits) t_lo = t; else t_hi = t - 1;
+    // Step 2: ATen's cumsum of the sorted 16-bit values: chunks of W = 2 * nx values; the running total enters
+    // the first value of a chunk; Sklansky combine steps, each sum rounded to the 16-bit type.
+    const int nx = 1 << scan_log_nx, W = 2 * nx;
+    auto add16 = [](uint16_t a, uint16_t b) -> uint16_t {
+      return (uint16_t)key_bits<T>(Elem<T>::from_float(__fadd_rn(key_value<T>(a), key_value<T>(b))));
+    };
+    uint16_t total = 0;
+    for (int c0 = 0; c0 < nk; c0 += W) {
+      uint16_t* buf = s_cdf + c0;
+      for (int i = lane; i < W; i += 32) buf[i] = (c0 + i < nk) ? (uint16_t)(s_sort[c0 + i] >> 16) : (uint16_t)0;
+      __syncwarp();
+      if (lane == 0) buf[0] = add16(buf[0], total);
+      __syncwarp();
+      for (int mm = 0; mm <= scan_log_nx; mm++) {
+        const int sgm = 1 << mm;
+        for (int t = lane; t < nx; t += 32) {
+          const int a = ((t >> mm) << (mm + 1)) | sgm;
+          const int ti = a + (t & (sgm - 1)), si = a - 1;
+          buf[ti] = add16(buf[ti], buf[si]);
+        }
+        __syncwarp();
       }
-      n_sel += t_lo;
+      total = buf[W - 1];
+      __syncwarp();
     }
+    // Step 3: torch.searchsorted(..., right=True): upper-bound binary search, 16-bit cdf compared in fp32
+    int lo_i = 0, hi_i = nk;
+    while (lo_i < hi_i) {
+      const int mid = lo_i + ((hi_i - lo_i) >> 1);
+      if (!(key_value<T>(s_cdf[mid]) > thr)) lo_i = mid + 1; else hi_i = mid;
+    }
+    n_sel = lo_i;
+    __syncwarp();
   }
   n_sel = max(1, min(n_sel, nk));
 
@@ -328,7 +359,12 @@ template <typename T, int D>
 static int launch_select(const void* pq, const void* pk, const uint8_t* sim_q, const uint8_t* sim_k, const float* topk,
                          const float* cdf, uint8_t* mask, int32_t* lut, int32_t* valid, int BH, int H, int nq, int nk,
                          int causal, int sink, int best_first, cudaStream_t st) {
-  const size_t row_bytes = select_row_bytes(nk, D);
+  // cdf mode reproduces torch.cumsum over the [B*H*nq, nk] matrix of sorted probabilities: the scan's chunking
+  // depends on both extents
+  const int scan_log_nx = aten_scan_log_threads_x((uint32_t)BH * (uint32_t)nq, (uint32_t)nk);
+  const int scan_w = 2 << scan_log_nx;
+  const int cdf_len = cdf ? (nk + scan_w - 1) / scan_w * scan_w : 0;
+  const size_t row_bytes = select_row_bytes(nk, D, cdf_len);
   const size_t tile_bytes = 32 * (D * sizeof(T) + 16);
   const size_t budget = 200 * 1024 - tile_bytes;
   if (row_bytes > budget) return SPARGE_ERR_TOO_LARGE;
@@ -340,7 +376,8 @@ static int launch_select(const void* pq, const void* pk, const uint8_t* sim_q, c
       return SPARGE_ERR_CUDA;
   }
   kern<<<dim3((nq + rows - 1) / rows, BH), kSelRowsPerCta * 32, smem, st>>>(
-      (const T*)pq, (const T*)pk, sim_q, sim_k, topk, cdf, mask, lut, valid, H, nq, nk, causal, sink, rows, best_first);
+      (const T*)pq, (const T*)pk, sim_q, sim_k, topk, cdf, mask, lut, valid, H, nq, nk, causal, sink, rows, best_first,
+      scan_log_nx, cdf_len);
   return launch_status();
 }
 

@@ -11,7 +11,9 @@ import sparge_oracle as O
 from make_golden import golden_inputs
 
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_predictor_*.pt")))
-GOLDEN_GPU = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_gpu_*.pt")))
+GOLDEN_GPU = sorted(p for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_gpu_*.pt"))
+                    if "_cdf_" not in os.path.basename(p))
+GOLDEN_GPU_CDF = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_gpu_cdf_*.pt")))
 
 
 def test_fixtures_present():
@@ -68,8 +70,28 @@ def test_oracle_matches_compiled_reference_fixture(path):
     assert m["Cossim"] >= 0.999 and m["L1"] <= 1e-2, m
 
 
+@pytest.mark.parametrize("path", GOLDEN_GPU_CDF, ids=[os.path.basename(p) for p in GOLDEN_GPU_CDF])
+def test_cdf_selection_matches_compiled_reference_fixture(path):
+    """cdf-threshold mode (spas_sage2_attn_meansim_cuda, what the reference's tuner calls) on rows of up to 512 blocks,
+    bf16 and fp16: the restated device cumsum equals torch's recorded output bit for bit, the restated search gives
+    torch's counts, and the oracle's block map equals the reference's."""
+    from make_ref_gpu_golden import ref_gpu_inputs
+    g = torch.load(path)
+    B, H, N, D, causal, cdf, sim1, seed = g["case"]
+    dtype = torch.bfloat16 if g["dtype"] == "bf16" else torch.float16
+    rows, n = g["sorted"].numel() // g["sorted"].shape[-1], g["sorted"].shape[-1]
+    em = O.aten_device_cumsum(g["sorted"].reshape(rows, n))
+    assert torch.equal(em.view(torch.int16), g["cdf"].reshape(rows, n).view(torch.int16))
+    assert torch.equal(O.searchsorted_right(em.float(), g["thr"].reshape(rows).float()), g["n_sel"].reshape(rows).long())
+    q, k, v = ref_gpu_inputs(B, H, N, D, dtype, seed)
+    assert abs(float(q.double().sum() + k.double().sum() + v.double().sum()) - g["input_sum"]) < 1e-6
+    pr = O.predictor(q, k, g["km"], causal, sim1, cdf, None, False)
+    assert torch.equal(pr["map"], g["map"]), f"{(pr['map'] != g['map']).sum().item()} of {g['map'].numel()} blocks differ"
+    assert torch.equal(pr["valid"], g["valid"])
+
+
 def test_compiled_reference_fixtures_present():
-    assert len(GOLDEN_GPU) >= 10
+    assert len(GOLDEN_GPU) >= 10 and len(GOLDEN_GPU_CDF) >= 6
 
 
 def _ref_block_map_lut(block_map):
