@@ -176,6 +176,25 @@ int sparge_attn_fwd_rows(const int8_t* q_int8, const int8_t* k_int8, const uint8
                          int is_causal, float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
                          int32_t* pv_count, const int32_t* q_block_ranges, int q_blocks_max, sparge_stream_t stream);
 
+/* sparge_attn_fwd_rows with the two remaining template arguments of the reference's kernel
+ * (csrc/qattn/attn_utils.cuh:45-63, dispatched at qk_int_sv_f8_cuda_sm89.cu:319-361):
+ *   qk_quant_gran  1 per block : q_scale [B,H,ceil(N/128)],      k_scale [B,H,ceil(N/64)]  (what the hot path passes)
+ *                  2 per warp  : q_scale [B,H,ceil(N/128)*4]  one per 32 query rows, k_scale as for 1
+ *                  3 per thread: q_scale [B,H,ceil(N/128)*32] entry (row/32)*8 + row%8 (rows r, r+8, r+16, r+24 of a
+ *                                32-row group share one), k_scale [B,H,ceil(N/64)*4] entry block*4 + (key%8)/2,
+ *                                16-byte aligned  (qk_int_sv_f8_cuda_sm89.cuh:106-136)
+ *   pv_threshold_mode  0 none (pvthreshd ignored), 1 per block (the one the reference's ops instantiate),
+ *                      2 per warp: each 32-row group decides for itself whether a block's P.V is dropped
+ *                        (qk_int_sv_f8_cuda_sm89.cuh:302-353 without the block-wide reduction); pv_count then
+ *                        differs between the four groups of a block.
+ * Other values: SPARGE_ERR_INVALID_ARG (the reference raises std::invalid_argument for an unknown granularity). */
+int sparge_attn_fwd_gran(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o, const int32_t* lut,
+                         const int32_t* valid, const float* pvthreshd, const float* q_scale, const float* k_scale,
+                         const float* v_scale, int32_t* dev_status, int B, int H, int N, int D, int out_dtype,
+                         int is_causal, float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
+                         int32_t* pv_count, const int32_t* q_block_ranges, int q_blocks_max, int qk_quant_gran,
+                         int pv_threshold_mode, sparge_stream_t stream);
+
 /* Failure-detection self test: launches one warp that waits on a barrier nobody signals, bounded by
  * slices x slice_ns nanoseconds (at most 0.1 s in total), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into
  * *dev_status when the bounded wait gives up -- the same code path that sparge_attn_fwd takes if a

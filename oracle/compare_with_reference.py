@@ -140,6 +140,50 @@ def compare(q, k, v, is_causal=False, topk=0.5, simthreshd1=-0.1, attention_sink
     return rep
 
 
+def compare_granularity(q, k, v, topk=0.5, pvthreshd=50.0) -> dict:
+    """qk_quant_gran 2 and 3 of the attention op. 2: the reference's Triton per_warp_int8 against this library's, then
+    both kernels on the reference's operands. 3: the reference ships no per-thread quantiser, so both kernels get the
+    CPU oracle's per-thread operands. Block map, LUT and FP8 V are the reference's own in both."""
+    B, H, N, D = q.shape
+    dev = q.device
+    rep = {"shape": [B, H, N, D], "dtype": str(q.dtype).replace("torch.", ""), "topk": topk, "pvthreshd": pvthreshd}
+    rq, rk, rv16, rkm = RR.prologue(q, k, v)
+    rp = RR.predictor(rq, rk, rkm, False, -0.1, None, topk, False, stable=True)
+    r_v8, r_vs, r_v8_tok = RR.quant_v(rv16)
+    pv_t = torch.full((H,), float(pvthreshd), dtype=torch.float32, device=dev)
+    pv_arg = pv_t if pvthreshd < 30 else None
+    sm = D ** -0.5
+    ksm = (rk - rkm).to(rk.dtype).contiguous()
+    # ---- granularity 2
+    q8r, qsr, k8r, ksr = RR.per_warp_int8(rq, ksm)
+    from spargeattn_b200 import core
+    q8, qs, k8, ks = core.per_warp_int8(rq, ksm)
+    qs, ks = qs.squeeze(-1), ks.squeeze(-1)
+    n_real = (N + 31) // 32                                     # groups that hold at least one row
+    rep["g2_q_int8_neq"], rep["g2_k_int8_neq"] = _neq(q8, q8r), _neq(k8, k8r)
+    rep["g2_q_scale_neq"], rep["g2_k_scale_neq"] = _neq(qs[..., :n_real], qsr[..., :n_real]), _neq(ks, ksr)
+    rep["g2_q_scale_tail_ref"] = [float(x) for x in qsr[0, 0, n_real:].tolist()]
+    rep["g2_q_scale_tail_ours"] = [float(x) for x in qs[0, 0, n_real:].tolist()]
+    r_o, r_cnt = RR.attention(q8r, k8r, r_v8, rp["lut"], rp["valid"], pv_t, qsr, ksr, r_vs, sm, q.dtype, qk_quant_gran=2,
+                              return_pv_count=True)
+    o, cnt = ops.attn_fwd(q8r, k8r, r_v8_tok, rp["lut"], rp["valid"], pv_arg, qsr, ksr, r_vs, sm, False, q.dtype,
+                          return_pv_count=True, qk_quant_gran=2)
+    rep["g2_attn_same_operands"] = metric(o, r_o)
+    rep["g2_pv_count_neq"], rep["g2_pv_count_total_ref"] = _neq(cnt, r_cnt), int(r_cnt.sum())
+    # the per-block result on the per-block operands, as a yardstick for what the finer scales change
+    o1 = ops.attn_fwd(rp["q_int8"], rp["k_int8"], r_v8_tok, rp["lut"], rp["valid"], pv_arg, rp["q_scale"], rp["k_scale"],
+                      r_vs, sm, False, q.dtype)
+    rep["g2_vs_g1_ours"] = metric(o, o1)
+    # ---- granularity 3
+    q8t, qst, k8t, kst = (t.to(dev) for t in O.per_thread_int8(rq.cpu(), ksm.cpu()))
+    r_o3 = RR.attention(q8t, k8t, r_v8, rp["lut"], rp["valid"], pv_t, qst, kst, r_vs, sm, q.dtype, qk_quant_gran=3)
+    o3 = ops.attn_fwd(q8t, k8t, r_v8_tok, rp["lut"], rp["valid"], pv_arg, qst, kst, r_vs, sm, False, q.dtype, qk_quant_gran=3)
+    rep["g3_attn_same_operands"] = metric(o3, r_o3)
+    rep["g3_vs_g1_ours"] = metric(o3, o1)
+    ops.check_device_status(dev)
+    return rep
+
+
 def oracle_vs_reference(q, k, v, is_causal, topk, simthreshd1=-0.1, attention_sink=False, cdfthreshd=None) -> dict:
     """CPU oracle against the reference's device results (small cases only)."""
     rq, rk, rv16, rkm = RR.prologue(q, k, v)
@@ -187,6 +231,21 @@ def main():
         r["case"] = "small-cdf"
         report["cases"].append(r)
         print(json.dumps(r), flush=True)
+    if "gran" in want:
+        for shape, dtype, pv in (((1, 2, 1000, 128), torch.bfloat16, 50.0), ((2, 2, 640, 64), torch.float16, 50.0),
+                                 ((1, 2, 3000, 64), torch.bfloat16, 4.0)):
+            q, k, v = (t.to(dev) for t in small_inputs(*shape, dtype, 12))
+            r = compare_granularity(q * (3 if pv < 30 else 1), k, v, topk=0.5, pvthreshd=pv)
+            r["case"] = "gran-small"
+            report["cases"].append(r)
+            print(json.dumps(r), flush=True)
+        q, k, v = synthetic.workload_qkv(2, dev, heads=2)
+        r = compare_granularity(q, k, v, topk=0.5)
+        r["case"] = "gran-cfg2"
+        report["cases"].append(r)
+        print(json.dumps(r), flush=True)
+        del q, k, v
+        torch.cuda.empty_cache()
     for idx, (heads, extra) in FULL.items():
         if f"cfg{idx}" not in want:
             continue

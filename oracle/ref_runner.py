@@ -133,13 +133,24 @@ def quant_v(v16: torch.Tensor):
     return v8, vs, token_major
 
 
-def attention(q8, k8, v_fp8, lut, valid, pvthreshd, q_scale, k_scale, v_scale, sm_scale, out_dtype, is_causal=False):
-    """core.py:155-156: the Sage2++ sm89 op (fp16 PV accumulation), per-block scales (qk_quant_gran = 1)."""
+def attention(q8, k8, v_fp8, lut, valid, pvthreshd, q_scale, k_scale, v_scale, sm_scale, out_dtype, is_causal=False,
+              qk_quant_gran=1, return_pv_count=False):
+    """core.py:155-156: the Sage2++ sm89 op (fp16 PV accumulation); the hot path passes per-block scales
+    (qk_quant_gran = 1), the op also takes per-warp (2) and per-thread (3) ones."""
     Q = load()["qattn"]
     o = torch.empty(q8.shape, dtype=out_dtype, device=q8.device)
-    Q.qk_int8_sv_f8_accum_f16_block_sparse_attn_inst_buf_fuse_v_scale_with_pv_threshold(
-        q8, k8, v_fp8, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, 1, int(bool(is_causal)), 1, float(sm_scale), 0)
-    return o
+    cnt = Q.qk_int8_sv_f8_accum_f16_block_sparse_attn_inst_buf_fuse_v_scale_with_pv_threshold(
+        q8, k8, v_fp8, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, 1, int(bool(is_causal)), int(qk_quant_gran),
+        float(sm_scale), int(bool(return_pv_count)))
+    return (o, cnt) if return_pv_count else o
+
+
+def per_warp_int8(q, k):
+    """quant_per_block.py:102-148 (Triton): INT8 Q with one scale per 32 rows, K with one per 64 keys."""
+    import importlib
+    mod = importlib.import_module(load()["core"].__package__ + ".quant_per_block")
+    q8, qs, k8, ks = mod.per_warp_int8(q, k)
+    return q8, qs.squeeze(-1).contiguous(), k8, ks.squeeze(-1).contiguous()
 
 
 def api_topk(q, k, v, stable: bool = True, **kw):

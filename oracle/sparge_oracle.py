@@ -390,8 +390,58 @@ def quant_v(v: torch.Tensor, recip_scale: Optional[torch.Tensor] = None) -> Tupl
 
 
 # ----------------------------------------------------------------------------- attention
+def per_warp_int8(q, k, BLKQ=128, WARPQ=32, BLKK=64, WARPK=64):
+    """spas_sage_attn/quant_per_block.py:102-148 (kernel :21-48, sm_scale = 1): one scale per WARPQ = 32 query rows
+    (ceil(N/128) * 4 per head; a group past the end gets 1e-7) and per WARPK = 64 keys; no mean subtraction.
+    HND layout.  Returns (q_int8, q_scale [B,H,nq*4], k_int8, k_scale [B,H,nk])."""
+    B, H, N, D = q.shape
+    _, _, q8, qs = pool_sim_quant(q, None, WARPQ, None, want_pool=False)
+    groups = (N + BLKQ - 1) // BLKQ * (BLKQ // WARPQ)
+    qs = torch.cat([qs, torch.full((B, H, groups - qs.shape[-1]), 1e-7, dtype=torch.float32)], -1)
+    _, _, k8, ks = pool_sim_quant(k, None, WARPK, None, want_pool=False)
+    return q8, qs, k8, ks
+
+
+def per_thread_int8(q, k, BLKQ=128, WARPQ=32, BLKK=64, WARPK=64):
+    """Quantiser for qk_quant_gran = 3.  The reference ships none (its kernel only documents the layout,
+    csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:116-136, scale shapes qk_int_sv_f8_cuda_sm89.cu:349-353): this one uses the
+    arithmetic of quant_per_block_int8_kernel on the row / key sets that share a scale -- rows r, r+8, r+16, r+24
+    of a 32-row group (entry (row // 32) * 8 + row % 8), keys 2t, 2t+1 of every 8 of a 64-key block (entry
+    block * 4 + (key % 8) // 2).  Returns (q_int8, q_scale [B,H,nq*32], k_int8, k_scale [B,H,nk*4])."""
+    B, H, N, D = q.shape
+
+    def quant(x, pad_to, shape, reduce_dims, group_of):
+        n_pad = (N + pad_to - 1) // pad_to * pad_to
+        x32 = torch.cat([x.float(), torch.zeros(B, H, n_pad - N, D)], 2)
+        amax = x32.abs().amax(-1).view(B, H, *shape).amax(dim=reduce_dims).reshape(B, H, -1)
+        scale = fma_f32(amax, torch.tensor(1.0, dtype=torch.float32) / 127.0, torch.tensor(1e-7, dtype=torch.float32))
+        y = x32 / scale[:, :, group_of(torch.arange(n_pad))].unsqueeze(-1)
+        y = y + torch.where(y >= 0, 0.5, -0.5).to(torch.float32)
+        return y.to(torch.int8)[:, :, :N].contiguous(), scale
+
+    # rows as (group of 32, which 8, row % 8); keys as (block of 64, which 8, pair in the 8, which of the pair)
+    q8, qs = quant(q, BLKQ, (-1, WARPQ // 8, 8), 3, lambda r: (r // WARPQ) * 8 + r % 8)
+    k8, ks = quant(k, BLKK, (-1, WARPK // 8, 4, 2), (3, 5), lambda n: (n // WARPK) * 4 + (n % 8) // 2)
+    return q8, qs, k8, ks
+
+
+def granular_scales(q_scale, k_scale, b, h, i, j, rows, cols, qk_quant_gran):
+    """Per-row and per-column dequantisation factors of scores tile (query block i, key block j) for the three
+    granularities of csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:106-136: 1 one scalar each; 2 one Q scale per 32 rows;
+    3 Q entry (row // 32) * 8 + row % 8 of the block's 32, K entry (key % 8) // 2 of the block's 4 (the mma.sync
+    accumulator layout of the reference: a thread owns rows r, r + 8 and key pairs 2t, 2t + 1 of every 8)."""
+    if qk_quant_gran == 1:
+        return q_scale[b, h, i].expand(rows), k_scale[b, h, j].expand(cols)
+    r = torch.arange(rows)
+    if qk_quant_gran == 2:
+        return q_scale[b, h, i * 4 + r // 32], k_scale[b, h, j].expand(cols)
+    n = torch.arange(cols)
+    return q_scale[b, h, i * 32 + (r // 32) * 8 + r % 8], k_scale[b, h, j * 4 + (n % 8) // 2]
+
+
 def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_scale: float, pvthreshd,
-                        token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True, q_blocks=None):
+                        token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True, q_blocks=None,
+                        qk_quant_gran: int = 1, pv_threshold_mode: int = 1, group_counts=None):
     """Oracle B: block-online emulation of csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:42-755 with the
     helpers of csrc/qattn/attn_utils.cuh (update_mo :418-466, exponentiate_r :391-415,
     RS_32_to_8 :581-596, normalize_d :757-811).  fp32 PV accumulation.
@@ -399,7 +449,12 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
     q8,k8: int8 [B,H,N,D]; q_scale [B,H,nq]; k_scale [B,H,nk]; v8: e4m3 values fp32 [B,H,N_pad,D];
     v_scale [B,H,D]; block_map bool [B,H,nq,nk]; pvthreshd fp32 [H].
     `q_blocks`: optional list of query-block indices; only those 128-row blocks are evaluated (the other
-    rows of the result stay zero), so that a sample of a long sequence can be checked in seconds."""
+    rows of the result stay zero), so that a sample of a long sequence can be checked in seconds.
+    `qk_quant_gran` 1/2/3: scale layouts of `granular_scales` (q_scale / k_scale then have 1/4/32 and 1/1/4
+    entries per block).  `pv_threshold_mode` 1: the skip test reduces over the 128-row block
+    (PVThresholdMode::kPerBlock, sm89.cuh:322-345); 2: every 32-row group decides for itself (kPerWarp: the
+    warp-level reduction of :317-320 only).  `group_counts`: optional int32 [B,H,nq*4] tensor that receives,
+    per 32-row group, the number of P.V products kept (the reference's PV_Count, sm89.cuh:355-358,650-656)."""
     B, H, N, D = q8.shape
     nq, nk = block_map.shape[-2:]
     c = sm_scale * LOG2E
@@ -419,7 +474,8 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
                 for n_it, j in enumerate(live):
                     c0, c1 = j * BLKK, min((j + 1) * BLKK, N)
                     s = qf @ kf[c0:c1].t()                              # exact: |S| < 2^24
-                    t = s * (c * q_scale[b, h, i] * k_scale[b, h, j])
+                    rs, cs = granular_scales(q_scale, k_scale, b, h, i, j, rows, c1 - c0, qk_quant_gran)
+                    t = s * ((c * rs).view(-1, 1) * cs.view(1, -1))
                     if token_causal:
                         qi = torch.arange(r0, r1).view(-1, 1)
                         kj = torch.arange(c0, c1).view(1, -1)
@@ -427,19 +483,30 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
                     rowmax = t.amax(dim=-1)
                     m_new = torch.maximum(m, rowmax)
                     is_tail = n_it >= len(live) - 2                    # last two live blocks never skip
+                    keep = torch.ones(rows, dtype=torch.bool)
                     if pv_skip and not is_tail:
-                        delta = (rowmax - m).max().item()
-                        if delta + float(pvthreshd[h]) <= 0:
-                            skipped += 1
-                            continue
+                        if pv_threshold_mode == 1:
+                            delta = (rowmax - m).max().item()
+                            if delta + float(pvthreshd[h]) <= 0:
+                                skipped += 1
+                                continue
+                        else:                                          # each 32-row group on its own
+                            for g0 in range(0, rows, 32):
+                                if (rowmax - m)[g0:g0 + 32].max().item() + float(pvthreshd[h]) <= 0:
+                                    keep[g0:g0 + 32] = False
+                                    skipped += 1
+                    if group_counts is not None:
+                        for g0 in range(0, BLKQ, 32):                  # a group past the end counts like its block
+                            if g0 >= rows or bool(keep[g0]):
+                                group_counts[b, h, i * 4 + g0 // 32] += 1
                     alpha = torch.exp2(m - m_new)
-                    d = d * alpha
-                    acc = acc * alpha.unsqueeze(-1)
-                    m = m_new
-                    p = torch.exp2(t - m.unsqueeze(-1) + S_FP8_OFFSET)
-                    d = d + p.sum(dim=-1)
-                    p8 = e4m3_round(p)
-                    acc = acc + p8 @ v8[b, h, c0:c1]
+                    p = torch.exp2(t - m_new.unsqueeze(-1) + S_FP8_OFFSET)
+                    d_new = d * alpha + p.sum(dim=-1)
+                    acc_new = acc * alpha.unsqueeze(-1) + e4m3_round(p) @ v8[b, h, c0:c1]
+                    # a group that drops the block keeps its state (its maximum cannot have risen: delta < 0)
+                    m = torch.where(keep, m_new, m)
+                    d = torch.where(keep, d_new, d)
+                    acc = torch.where(keep.unsqueeze(-1), acc_new, acc)
                 if live:
                     o[b, h, r0:r1] = acc / d.unsqueeze(-1) * v_scale[b, h].view(1, D)
     return o.to(out_dtype), skipped

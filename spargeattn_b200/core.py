@@ -124,6 +124,22 @@ def get_vanilla_qk_quant(q, k, km=None, BLKQ=128, BLKK=64):
     return q_int8, q_scale, k_int8, k_scale
 
 
+def per_warp_int8(q, k, BLKQ=128, WARPQ=32, BLKK=64, WARPK=64, tensor_layout="HND"):
+    """spas_sage_attn/quant_per_block.py:102-148 -- INT8 Q with one scale per 32 rows, K with one per 64 keys (the
+    operands of qk_quant_gran = 2); no mean subtraction. Returns (q_int8, q_scale [B,H,ceil(N/128)*4,1], k_int8,
+    k_scale [B,H,ceil(N/64),1]); the INT8 tensors have the inputs' shape."""
+    assert (BLKQ, WARPQ, BLKK, WARPK) == (128, 32, 64, 64), "the attention kernel's tiling: 128/32 query rows, 64 keys"
+    if tensor_layout not in ("HND", "NHD"):
+        raise ValueError(f"Unknown tensor layout: {tensor_layout}")
+    if tensor_layout == "NHD":
+        q, k = q.transpose(1, 2), k.transpose(1, 2)
+    _, _, q_int8, q_scale = ops.pool_sim_quant(q, None, WARPQ, None)
+    _, _, k_int8, k_scale = ops.pool_sim_quant(k, None, WARPK, None)
+    if tensor_layout == "NHD":
+        q_int8, k_int8 = q_int8.transpose(1, 2), k_int8.transpose(1, 2)
+    return q_int8, q_scale.unsqueeze(-1), k_int8, k_scale.unsqueeze(-1)
+
+
 def block_map_lut_triton(block_map):
     """spas_sage_attn/utils.py:76-87 (name kept for callers; nothing here uses Triton)."""
     return ops.mask_to_lut(block_map)

@@ -96,6 +96,41 @@ __device__ __forceinline__ float chunk_rowmax(const uint32_t* sr, float c, int k
   }
 }
 
+// Per-thread granularity (QuantGranularity::kPerThread, qk_int_sv_f8_cuda_sm89.cuh:116-136): key column n of a
+// block is scaled by entry (n % 8) / 2 of the block's four K scales, so a thread's 32 scores carry four different
+// factors c4[0..3] and the integer maximum no longer commutes with the scaling: one maximum per factor.
+__device__ __forceinline__ float chunk_rowmax_g(const uint32_t* sr, const float* c4, int klim) {
+  int mx[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+#pragma unroll
+  for (int k = 0; k < 32; k++) mx[(k & 7) >> 1] = (k < klim) ? max(mx[(k & 7) >> 1], (int)sr[k]) : mx[(k & 7) >> 1];
+  float r = kMaskValue;
+#pragma unroll
+  for (int g = 0; g < 4; g++) r = (mx[g] != INT_MIN) ? fmaxf(r, __int2float_rn(mx[g]) * c4[g]) : r;
+  return r;
+}
+
+__device__ __forceinline__ float chunk_exp_g(const uint32_t* sr, const float* c4, float m, int klim, uint32_t prow,
+                                             int chunk0, int rsw) {
+  uint32_t pr[4];
+  const float off = kFp8Offset - m;
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < 32; k += 4) {
+    float p0 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 0]), c4[((k + 0) & 7) >> 1], off));
+    float p1 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 1]), c4[((k + 1) & 7) >> 1], off));
+    float p2 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 2]), c4[((k + 2) & 7) >> 1], off));
+    float p3 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 3]), c4[((k + 3) & 7) >> 1], off));
+    p0 = (k + 0 < klim) ? p0 : 0.f;
+    p1 = (k + 1 < klim) ? p1 : 0.f;
+    p2 = (k + 2 < klim) ? p2 : 0.f;
+    p3 = (k + 3 < klim) ? p3 : 0.f;
+    sum += (p0 + p1) + (p2 + p3);
+    pr[(k >> 2) & 3] = cvt_e4m3x4(p0, p1, p2, p3);
+    if ((k & 12) == 12) st_shared_v4(prow + (uint32_t)(((chunk0 + (k >> 4)) ^ rsw) << 4), pr);
+  }
+  return sum;
+}
+
 // P = 2^(S*c - m + 8.807) for 32 scores: row sum in fp32 before the e4m3 rounding
 // (ComputeUnit::kCudaCore, qk_int_sv_f8_cuda_sm89.cuh:773), bytes stored to the row's two 16-byte chunks
 // chunk0, chunk0+1 of the 128B-swizzled P tile. `prow` = shared address of the row, rsw = row & 7.
@@ -163,7 +198,10 @@ __device__ __forceinline__ void pair_sync(int id) {   // the two warps that shar
 
 constexpr int kAttnThreads = 320;
 
-template <int D, bool CAUSAL, bool PV_SKIP, typename OutT>
+// GRAN = qk_quant_gran: 1 one Q scale per 128-row block, 2 one per 32-row group (the K scale is per 64-key block in
+// both), 3 per-thread Q/K scales. PV_MODE = PVThresholdMode: 0 no skip test, 1 the test decides per block, 2 per
+// 32-row group.
+template <int D, bool CAUSAL, int PV_MODE, typename OutT, int GRAN>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
             const __grid_constant__ CUtensorMap tmap_v, OutT* __restrict__ o, const int32_t* __restrict__ lut,
@@ -172,6 +210,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
             int nq, int nk, float sm_scale_log2, int one, long long osb, long long osh, long long osn,
             int32_t* __restrict__ pv_count, const int32_t* __restrict__ q_ranges) {
   using Shape = AttnShape<D>;
+  constexpr bool PV_SKIP = PV_MODE != 0, pv_per_warp = PV_MODE == 2, GRAN3 = GRAN == 3;
   constexpr int SK = Shape::kStagesK, SV = Shape::kStagesV;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -416,7 +455,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     const uint32_t tlane = (uint32_t)(wq * 32) << 16;
     const uint32_t tS = tbase + tlane;
     const int qrow = qi * 128 + row;
-    const float qs = q_scale[row_id] * sm_scale_log2;
+    const float qs = (GRAN3 ? q_scale[row_id * 32 + wq * 8 + (lane & 7)]
+                            : q_scale[GRAN == 1 ? row_id : row_id * 4 + wq]) * sm_scale_log2;
+    const float* ks_row = k_scale + (size_t)bh * nk * 4;   // GRAN3 only: four K scales per block
     const float thr = PV_SKIP ? pvthr[h] : 0.f;
     const uint32_t prow = smem_u32(sP) + (uint32_t)row * 128u;
     const int rsw = row & 7;
@@ -435,6 +476,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       const bool second = (nb == 2) && half;
       const int j = second ? mt.y : mt.x;
       const float c = qs * __int_as_float(second ? mt.w : mt.z);
+      float c4[4];
+      if (GRAN3) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks_row + (size_t)j * 4);
+        c4[0] = qs * k4.x; c4[1] = qs * k4.y; c4[2] = qs * k4.z; c4[3] = qs * k4.w;
+      }
       // per-key mask limit of this row inside the block: keys with block-local index >= klim are masked
       const int key0 = j * 64;
       const bool masked = (key0 + 64 > N) || (CAUSAL && (key0 + 63 > qi * 128));
@@ -448,11 +494,13 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       uint32_t sr[32];
       tmem_ld32(tS + col0, sr);
       tmem_wait_ld();
-      float rmax = masked ? chunk_rowmax<true>(sr, c, klim - kofs) : chunk_rowmax<false>(sr, c, 32);
+      float rmax = GRAN3 ? chunk_rowmax_g(sr, c4, klim - kofs)
+                         : masked ? chunk_rowmax<true>(sr, c, klim - kofs) : chunk_rowmax<false>(sr, c, 32);
       if (nch == 2) {
         tmem_ld32(tS + col0 + 32, sr);
         tmem_wait_ld();
-        rmax = fmaxf(rmax, masked ? chunk_rowmax<true>(sr, c, klim - kofs - 32) : chunk_rowmax<false>(sr, c, 32));
+        rmax = fmaxf(rmax, GRAN3 ? chunk_rowmax_g(sr, c4, klim - kofs - 32)
+                                 : masked ? chunk_rowmax<true>(sr, c, klim - kofs - 32) : chunk_rowmax<false>(sr, c, 32));
       }
       // exchange the partial row maxima of the two threads of a row
       s_rmax[s & 1][half][row] = rmax;
@@ -465,6 +513,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       // publish their partial maxima now and read the result only after the exponentials, so the reduction
       // latency is hidden; the last two live blocks are never skipped.
       const bool candA = PV_SKIP && (2 * s < cnt - 2), candB = PV_SKIP && (nb == 2) && (2 * s + 1 < cnt - 2);
+      bool own_skip = false;   // per-warp mode: this warp's 32 rows drop their block (known before the exponentials)
       if (PV_SKIP && (candA || candB)) {
         // half 0 publishes block A's delta, half 1 block B's (a single-block step cannot be a candidate)
         const float w = warp_max(half ? (r1 - m1) : (r0 - m));
@@ -472,6 +521,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
           s_delta[s & 1][half][wq] = w;
           mbar_arrive(&bar_delta[s & 1]);
         }
+        own_skip = pv_per_warp && (half ? candB : candA) && (w + thr <= 0.f);
       }
       const float alpha = (s > 0) ? ex2_approx(m - m2) : 0.f;
       const bool need_rescale = (s > 0) && __any_sync(0xffffffffu, m2 > m);
@@ -502,11 +552,15 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       }
       d *= alpha;
       m = m2;
-      const bool exact = masked || !(c < kFastScaleLimit);
+      // A 32-row group that drops its block in per-warp mode still writes its rows of P (as zeros, through the
+      // masked path with no visible key): the other groups' rows of the same block may be multiplied.
+      if (PV_SKIP && own_skip) klim = 0;
+      const bool exact = masked || own_skip || !(c < kFastScaleLimit);
       float sum = 0.f;
       if (nch == 2) {   // the second 32 columns are still in registers
-        sum = exact ? chunk_exp<true>(sr, c, m, klim - kofs - 32, one, prow, (col0 >> 4) + 2, rsw)
-                    : chunk_exp<false>(sr, c, m, 32, one, prow, (col0 >> 4) + 2, rsw);
+        sum = GRAN3 ? chunk_exp_g(sr, c4, m, klim - kofs - 32, prow, (col0 >> 4) + 2, rsw)
+              : exact ? chunk_exp<true>(sr, c, m, klim - kofs - 32, one, prow, (col0 >> 4) + 2, rsw)
+                      : chunk_exp<false>(sr, c, m, 32, one, prow, (col0 >> 4) + 2, rsw);
         tmem_ld32(tS + col0, sr);            // the first 32 again: they did not stay in registers
         tmem_wait_ld();
       }
@@ -514,8 +568,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_s_free);
-      sum += exact ? chunk_exp<true>(sr, c, m, klim - kofs, one, prow, col0 >> 4, rsw)
-                   : chunk_exp<false>(sr, c, m, 32, one, prow, col0 >> 4, rsw);
+      sum += GRAN3 ? chunk_exp_g(sr, c4, m, klim - kofs, prow, col0 >> 4, rsw)
+             : exact ? chunk_exp<true>(sr, c, m, klim - kofs, one, prow, col0 >> 4, rsw)
+                     : chunk_exp<false>(sr, c, m, 32, one, prow, col0 >> 4, rsw);
       bool skip = false;
       if (PV_SKIP && (candA || candB)) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bar_delta[s & 1], (s >> 1) & 1));
@@ -524,18 +579,21 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         const float* db = s_delta[s & 1][1];
         const bool skipA = candA && (fmaxf(fmaxf(da[0], da[1]), fmaxf(da[2], da[3])) + thr <= 0.f);
         const bool skipB = candB && (fmaxf(fmaxf(db[0], db[1]), fmaxf(db[2], db[3])) + thr <= 0.f);
-        skip = half ? skipB : skipA;         // candidates only occur in two-block steps: one block per thread
+        // candidates only occur in two-block steps: one block per thread. The product itself is left out only
+        // when all four groups drop the block, which is the per-block decision in either mode.
+        skip = pv_per_warp ? own_skip : (half ? skipB : skipA);
         if (tid == 0) {
           s_skip[0] = skipA ? 1 : 0;
           s_skip[1] = skipB ? 1 : 0;
         }
-        npv += (skipA ? 0 : 1) + (skipB ? 0 : 1);
+        // per-warp mode counts this warp's own block; the two warps of a group are added up at the end
+        npv += pv_per_warp ? (own_skip ? 0 : 1) : (skipA ? 0 : 1) + (skipB ? 0 : 1);
       } else {
         if (PV_SKIP && tid == 0) {
           s_skip[0] = 0;
           s_skip[1] = 0;
         }
-        npv += nb;
+        npv += pv_per_warp ? (nb == 2 ? 1 : 1 - half) : nb;
       }
       if (!skip) d += sum;
       fence_proxy_async_smem();      // P bytes visible to the tensor core's operand fetch
@@ -546,12 +604,15 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bar_o_done, (nsteps - 1) & 1));
     if (ok) {
       tc_fence_after();
-      // One count per 32-row group, the layout of the reference's PV_Count (qk_int_sv_f8_cuda_sm89.cuh:650-656);
-      // the skip decision is taken per block, so the four entries of a block are equal.
-      if (pv_count && lane == 0 && half == 0) pv_count[row_id * 4 + wq] = npv;
       // total row sum = the two threads' partial sums
       s_rmax[0][half][row] = d;
+      if (PV_SKIP && pv_per_warp) s_rmax[1][half][row] = __int_as_float(npv);
       pair_sync(1 + wq);
+      // One count per 32-row group, the layout of the reference's PV_Count (qk_int_sv_f8_cuda_sm89.cuh:650-656).
+      // With the per-block decision the four entries of a block are equal; with the per-warp decision each group
+      // has its own, the sum of what its two warps (one per block of a pair) kept.
+      if (PV_SKIP && pv_per_warp) npv = __float_as_int(s_rmax[1][0][row]) + __float_as_int(s_rmax[1][1][row]);
+      if (pv_count && lane == 0 && half == 0) pv_count[row_id * 4 + wq] = npv;
       const float inv = rcp_approx(s_rmax[0][0][row] + s_rmax[0][1][row]);
       const float* vs = v_scale + (size_t)bh * D + half * (D / 2);
       OutT* orow = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qrow * osn + half * (D / 2);
@@ -612,12 +673,12 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t r
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, bool CAUSAL, bool PV_SKIP, typename OutT>
+template <int D, bool CAUSAL, int PV_MODE, typename OutT, int GRAN>
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, const int32_t* lut,
                        const int32_t* valid, const float* pvthr, const float* qs, const float* ks, const float* vs,
                        int32_t* status, int BH, int H, int N, float sm_scale_log2, long long osb, long long osh,
                        long long osn, int32_t* pv_count, const int32_t* q_ranges, int q_blocks_max, cudaStream_t st) {
-  auto kern = attn_kernel<D, CAUSAL, PV_SKIP, OutT>;
+  auto kern = attn_kernel<D, CAUSAL, PV_MODE, OutT, GRAN>;
   constexpr int smem = AttnShape<D>::kSmemBytes;
   // function attributes are per device: set on every call (cheap) rather than caching
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return SPARGE_ERR_CUDA;
@@ -652,15 +713,21 @@ extern "C" int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int sli
   return sparge::launch_status();
 }
 
-extern "C" int sparge_attn_fwd_rows(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
+extern "C" int sparge_attn_fwd_gran(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
                                     const int32_t* lut, const int32_t* valid, const float* pvthreshd,
                                     const float* q_scale, const float* k_scale, const float* v_scale,
                                     int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
                                     float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
                                     int32_t* pv_count, const int32_t* q_block_ranges, int q_blocks_max,
-                                    sparge_stream_t stream) {
+                                    int qk_quant_gran, int pv_threshold_mode, sparge_stream_t stream) {
   using namespace sparge;
   if (q_block_ranges && q_blocks_max <= 0) return SPARGE_ERR_INVALID_ARG;
+  if (qk_quant_gran < 1 || qk_quant_gran > 3 || pv_threshold_mode < 0 || pv_threshold_mode > 2) return SPARGE_ERR_INVALID_ARG;
+  if (pv_threshold_mode == 0) pvthreshd = nullptr;
+  else if (!pvthreshd) return SPARGE_ERR_NULL;
+  // per-thread K scales are read four at a time
+  if (qk_quant_gran == 3 && (reinterpret_cast<uintptr_t>(k_scale) & 15)) return SPARGE_ERR_INVALID_ARG;
+
   if (!q_int8 || !k_int8 || !v8 || !o || !lut || !valid || !q_scale || !k_scale || !v_scale) return SPARGE_ERR_NULL;
   if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (out_dtype != SPARGE_F16 && out_dtype != SPARGE_BF16))
     return SPARGE_ERR_INVALID_ARG;
@@ -674,17 +741,33 @@ extern "C" int sparge_attn_fwd_rows(const int8_t* q_int8, const int8_t* k_int8, 
     return SPARGE_ERR_CUDA;
   cudaStream_t st = (cudaStream_t)stream;
   const float sl2 = sm_scale * kLog2e;
-  const bool causal = is_causal != 0, skip = pvthreshd != nullptr, bf = out_dtype == SPARGE_BF16;
+  const bool causal = is_causal != 0, bf = out_dtype == SPARGE_BF16;
+#define SPARGE_ATTN_G(DD, C, S, T, G) \
+  launch_attn<DD, C, S, T, G>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, BH, H, N, sl2, o_stride_b, o_stride_h, o_stride_n, pv_count, q_block_ranges, q_blocks_max, st)
 #define SPARGE_ATTN(DD, C, S, T) \
-  launch_attn<DD, C, S, T>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, BH, H, N, sl2, o_stride_b, o_stride_h, o_stride_n, pv_count, q_block_ranges, q_blocks_max, st)
+  (qk_quant_gran == 3 ? SPARGE_ATTN_G(DD, C, S, T, 3) : qk_quant_gran == 2 ? SPARGE_ATTN_G(DD, C, S, T, 2) : SPARGE_ATTN_G(DD, C, S, T, 1))
 #define SPARGE_ATTN_T(DD, C, S) (bf ? SPARGE_ATTN(DD, C, S, __nv_bfloat16) : SPARGE_ATTN(DD, C, S, __half))
-#define SPARGE_ATTN_S(DD, C) (skip ? SPARGE_ATTN_T(DD, C, true) : SPARGE_ATTN_T(DD, C, false))
+#define SPARGE_ATTN_S(DD, C) \
+  (pv_threshold_mode == 2 ? SPARGE_ATTN_T(DD, C, 2) : pv_threshold_mode == 1 ? SPARGE_ATTN_T(DD, C, 1) : SPARGE_ATTN_T(DD, C, 0))
 #define SPARGE_ATTN_C(DD) (causal ? SPARGE_ATTN_S(DD, true) : SPARGE_ATTN_S(DD, false))
   return D == 64 ? SPARGE_ATTN_C(64) : SPARGE_ATTN_C(128);
 #undef SPARGE_ATTN_C
 #undef SPARGE_ATTN_S
 #undef SPARGE_ATTN_T
 #undef SPARGE_ATTN
+#undef SPARGE_ATTN_G
+}
+
+extern "C" int sparge_attn_fwd_rows(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,
+                                    const int32_t* lut, const int32_t* valid, const float* pvthreshd,
+                                    const float* q_scale, const float* k_scale, const float* v_scale,
+                                    int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal,
+                                    float sm_scale, long long o_stride_b, long long o_stride_h, long long o_stride_n,
+                                    int32_t* pv_count, const int32_t* q_block_ranges, int q_blocks_max,
+                                    sparge_stream_t stream) {
+  return sparge_attn_fwd_gran(q_int8, k_int8, v8, o, lut, valid, pvthreshd, q_scale, k_scale, v_scale, dev_status, B, H, N, D,
+                              out_dtype, is_causal, sm_scale, o_stride_b, o_stride_h, o_stride_n, pv_count, q_block_ranges,
+                              q_blocks_max, 1, pvthreshd ? 1 : 0, stream);
 }
 
 extern "C" int sparge_attn_fwd_pv_count(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,

@@ -1,7 +1,9 @@
 // One pass over Q (128-row blocks) or K (64-row blocks): optional mean subtraction in the
 // 16-bit type, block pooling, cosine self-similarity flag and per-block INT8 quantisation.
 // Replaces triton_bmm_pool_sim_simmean_fuse_quant (spas_sage_attn/utils.py:161-214) and
-// qk_quantize (utils.py:89-159).
+// qk_quantize (utils.py:89-159). With 32-row blocks and no pooling it is the Q half of the per-warp
+// quantiser (per_warp_int8, spas_sage_attn/quant_per_block.py:102-148: one scale per 32 query rows,
+// ceil(N/128)*4 scales per head, 1e-7 for groups past the end).
 //
 // Arithmetic contract (shared with the CPU oracle):
 //   * row sums (pool, sum of unit vectors): fp32 running sum over each run of 8 consecutive rows,
@@ -57,7 +59,7 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
   const int cg = tid % TPR, g = tid / TPR;
   const int blk = blockIdx.x, bh = blockIdx.y;
   const int row_base = blk * BS;
-  const int rows_here = min(BS, N - row_base);
+  const int rows_here = max(0, min(BS, N - row_base));   // 0: a 32-row group past the end (scale 1e-7, nothing else)
   const T* xb = x + (size_t)(bh / H) * sb + (size_t)(bh % H) * sh + (size_t)row_base * sn;
 
   float kmv[8];
@@ -198,7 +200,7 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
 template <typename T, int D, int BS>
 static int launch_pq(const void* x, const void* km, const float* thr, void* pool, uint8_t* sim, int8_t* xq, float* sc,
                      int BH, int H, int N, long long sb, long long sh, long long sn, cudaStream_t st) {
-  const int nb = (N + BS - 1) / BS;
+  const int nb = BS == 32 ? (N + 127) / 128 * 4 : (N + BS - 1) / BS;
   dim3 grid(nb, BH);
   const bool has_km = km != nullptr, want = thr != nullptr;
 #define SPARGE_PQ(KM, WP)                                                                                         \
@@ -215,6 +217,8 @@ static int launch_pq(const void* x, const void* km, const float* thr, void* pool
 template <typename T>
 static int dispatch_pq(const void* x, const void* km, const float* thr, void* pool, uint8_t* sim, int8_t* xq, float* sc,
                        int BH, int H, int N, int D, int block, long long sb, long long sh, long long sn, cudaStream_t st) {
+  if (D == 64 && block == 32) return launch_pq<T, 64, 32>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
+  if (D == 128 && block == 32) return launch_pq<T, 128, 32>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
   if (D == 64 && block == 128) return launch_pq<T, 64, 128>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
   if (D == 64 && block == 64) return launch_pq<T, 64, 64>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
   if (D == 128 && block == 128) return launch_pq<T, 128, 128>(x, km, thr, pool, sim, xq, sc, BH, H, N, sb, sh, sn, st);
@@ -230,9 +234,10 @@ extern "C" int sparge_pool_quant_strided(const void* x, const void* km, const fl
   using namespace sparge;
   if (!x || !x_int8 || !scale) return SPARGE_ERR_NULL;
   if (simthreshd1 && (!pool || !sim)) return SPARGE_ERR_NULL;
-  if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (block != 64 && block != 128) ||
+  if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (block != 32 && block != 64 && block != 128) ||
       (dtype != SPARGE_F16 && dtype != SPARGE_BF16))
     return SPARGE_ERR_INVALID_ARG;
+  if (block == 32 && simthreshd1) return SPARGE_ERR_UNSUPPORTED;   // 32-row groups are a quantiser granularity only
   if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;
   if (!strides_ok(x, stride_b, stride_h, stride_n)) return SPARGE_ERR_INVALID_ARG;
   cudaStream_t st = (cudaStream_t)stream;

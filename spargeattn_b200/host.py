@@ -44,6 +44,10 @@ def spas_sage2_attn_meansim_topk_host(q: torch.Tensor, k: torch.Tensor, v: torch
     pipe = _pipes.setdefault(dev.index, _Pipe(dev))
     hc = max(1, min(heads_per_chunk, H))
     chunks = [(b, h0, min(h0 + hc, H)) for b in range(B) for h0 in range(0, H, hc)]
+    # Uploads run back to back, so the call ends one compute and one download after the last upload: the last
+    # chunk goes head by head, which makes that tail as short as it can be.
+    b, h0, h1 = chunks.pop()
+    chunks += [(b, h, h + 1) for h in range(h0, h1)]
     nbuf = 3
     dq = pipe.buffers("q", (1, hc, N, D), q.dtype, dev, nbuf)
     dk = pipe.buffers("k", (1, hc, N, D), k.dtype, dev, nbuf)

@@ -83,7 +83,8 @@ def pool_sim_quant(x: torch.Tensor, km: Optional[torch.Tensor], block: int, simt
     _need_strided(x)
     _need_cuda(km, simthreshd1)
     B, H, N, D = x.shape
-    nb = (N + block - 1) // block
+    # 32-row groups (per-warp granularity of Q, quantiser only) are counted per 128-row block: four each
+    nb = (N + 127) // 128 * 4 if block == 32 else (N + block - 1) // block
     x8 = torch.empty(B, H, N, D, dtype=torch.int8, device=x.device)
     scale = torch.empty(B, H, nb, dtype=torch.float32, device=x.device)
     pool = sim = None
@@ -151,11 +152,14 @@ def div_approx(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale, k_scale, v_scale, sm_scale: float,
              is_causal: bool, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
-             return_pv_count: bool = False, q_block_ranges: Optional[torch.Tensor] = None, q_blocks_max: int = 0):
+             return_pv_count: bool = False, q_block_ranges: Optional[torch.Tensor] = None, q_blocks_max: int = 0,
+             qk_quant_gran: int = 1, pv_threshold_mode: Optional[int] = None):
     """Block-sparse attention. With `return_pv_count` also returns int32 [B, H, ceil(N/128)*4]: per 32-row group the
     number of P.V products computed (the `return_pv_count` diagnostic of csrc/qattn/qk_int_sv_f8_cuda_sm89.cu:526-584).
     `q_block_ranges` (int32 [B, H, 2] on the device: first query block, count) restricts each head to a range of
-    128-row query blocks; the other rows of the output are left untouched. `q_blocks_max` >= the largest count."""
+    128-row query blocks; the other rows of the output are left untouched. `q_blocks_max` >= the largest count.
+    `qk_quant_gran` 1 / 2 / 3: per-block, per-warp or per-thread Q/K scales; `pv_threshold_mode` 0 none, 1 per block,
+    2 per 32-row group (default: 1 when `pvthreshd` is given, else 0) -- csrc/qattn/attn_utils.cuh:45-63."""
     _need_cuda(q8, k8, v8, lut, valid, pvthreshd, q_scale, k_scale, v_scale, q_block_ranges)
     B, H, N, D = q8.shape
     if out is None:
@@ -165,11 +169,19 @@ def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale,
     pv_count = torch.empty(B, H, (N + 127) // 128 * 4, dtype=torch.int32, device=q8.device) if return_pv_count else None
     if q_block_ranges is not None:
         assert q_block_ranges.dtype == torch.int32 and q_block_ranges.numel() == 2 * B * H and q_blocks_max > 0
-    _cabi.check(_cabi.lib.sparge_attn_fwd_rows(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
+    if pv_threshold_mode is None:
+        pv_threshold_mode = 0 if pvthreshd is None else 1
+    nq, nk = (N + 127) // 128, (N + 63) // 64
+    want = {1: (nq, nk), 2: (nq * 4, nk), 3: (nq * 32, nk * 4)}.get(qk_quant_gran)
+    if want is None:
+        raise ValueError(f"Unsupported qk_quant_gran: {qk_quant_gran}")      # as DISPATCH_QK_QUANT_GRAN does
+    assert q_scale.numel() == B * H * want[0] and k_scale.numel() == B * H * want[1], "scale shapes do not match qk_quant_gran"
+    _cabi.check(_cabi.lib.sparge_attn_fwd_gran(_ptr(q8), _ptr(k8), _ptr(v8), _ptr(out), _ptr(lut), _ptr(valid),
                                                _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(v_scale),
                                                _ptr(status), B, H, N, D, _dt(out), int(bool(is_causal)),
                                                float(sm_scale), out.stride(0), out.stride(1), out.stride(2),
-                                               _ptr(pv_count), _ptr(q_block_ranges), int(q_blocks_max), _stream(q8)),
+                                               _ptr(pv_count), _ptr(q_block_ranges), int(q_blocks_max),
+                                               int(qk_quant_gran), int(pv_threshold_mode), _stream(q8)),
                 "sparge_attn_fwd")
     return (out, pv_count) if return_pv_count else out
 

@@ -36,7 +36,9 @@ def test_null_and_bad_arguments_return_status_codes():
     assert L.sparge_k_mean(one, one, one, 1, 1, 128, 96, 0, None) == _cabi.ERR_INVALID_ARG
     assert L.sparge_k_mean(one, one, one, 1, 1, 128, 64, 7, None) == _cabi.ERR_INVALID_ARG
     assert L.sparge_pool_quant(one, None, None, None, None, None, one, 1, 1, 128, 64, 128, 0, None) == _cabi.ERR_NULL
-    assert L.sparge_pool_quant(one, None, None, None, None, one, one, 1, 1, 128, 64, 32, 0, None) == _cabi.ERR_INVALID_ARG
+    assert L.sparge_pool_quant(one, None, None, None, None, one, one, 1, 1, 128, 64, 48, 0, None) == _cabi.ERR_INVALID_ARG
+    # 32-row groups are a quantiser granularity (per-warp Q scales): no pooling / self-similarity for them
+    assert L.sparge_pool_quant(one, None, one, one, one, one, one, 1, 1, 128, 64, 32, 0, None) == _cabi.ERR_UNSUPPORTED
     assert L.sparge_pool_quant(one, None, one, None, None, one, one, 1, 1, 128, 64, 64, 0, None) == _cabi.ERR_NULL
     assert L.sparge_select(one, one, one, one, one, one, None, one, one, 1, 1, 1, 2, 64, 0, 0, 0, 0, None) == _cabi.ERR_INVALID_ARG
     assert L.sparge_select(one, one, one, one, None, None, None, one, one, 1, 1, 1, 2, 64, 0, 0, 0, 0, None) == _cabi.ERR_INVALID_ARG
@@ -47,6 +49,13 @@ def test_null_and_bad_arguments_return_status_codes():
         == _cabi.ERR_INVALID_ARG
     assert L.sparge_attn_fwd(one, one, one, None, one, one, None, one, one, one, None, 1, 1, 128, 64, 1, 0, 0.125, None) \
         == _cabi.ERR_NULL
+    gran = lambda g, mode, thr: L.sparge_attn_fwd_gran(one, one, one, one, one, one, thr, one, one, one, None, 1, 1, 128, 64, 1, 0,
+                                                       0.125, 8192, 8192, 64, None, None, 0, g, mode, None)
+    assert gran(0, 0, None) == _cabi.ERR_INVALID_ARG and gran(4, 0, None) == _cabi.ERR_INVALID_ARG   # unknown granularity
+    assert gran(1, 3, None) == _cabi.ERR_INVALID_ARG                                                   # unknown skip mode
+    assert gran(2, 2, None) == _cabi.ERR_NULL                                                          # a mode without thresholds
+    assert L.sparge_attn_fwd_gran(one, one, one, one, one, one, None, one, ctypes.c_void_p(20), one, None, 1, 1, 128, 64, 1, 0,
+                                  0.125, 8192, 8192, 64, None, None, 0, 3, 0, None) == _cabi.ERR_INVALID_ARG   # K scales not 16-byte aligned
     assert L.sparge_k_mean_scratch_bytes(1, 12, 32760, 128) == 12 * 64 * 128 * 8
     with pytest.raises(ValueError):
         _cabi.check(_cabi.ERR_INVALID_ARG, "x")

@@ -271,3 +271,106 @@ def test_row_range_units_equal_the_full_call(D, causal):
     from spargeattn_b200 import core
     o = attention_units(q, k, v, buf_ranges, topk=0.5, is_causal=causal)
     assert torch.equal(o[:, :, 256:640], full[:, :, 256:640])
+
+
+def _gran_case(N, D, dtype, seed, gran, topk=0.6, causal=False):
+    """Operands for the attention entry with per-block / per-warp / per-thread Q/K scales: the block map of the
+    predictor, the quantised operands of the granularity's quantiser, FP8 V -- all from the oracle."""
+    B, H = 1, 2
+    q, k, v = _inputs(B, H, N, D, dtype, seed)
+    q = q * 3                                              # peaky softmax: the skip test has something to drop
+    km = O.k_mean(k)
+    pr = O.predictor(q, k, km, causal, torch.full((H,), -0.1), None, torch.full((H,), topk), False)
+    ksm = (k - km).to(dtype)
+    if gran == 1:
+        q8, qs, k8, ks = pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"]
+    elif gran == 2:
+        q8, qs, k8, ks = O.per_warp_int8(q, ksm)
+    else:
+        q8, qs, k8, ks = O.per_thread_int8(q, ksm)
+    v8, vs = O.quant_v(v)
+    lut, valid = O.block_map_to_lut(pr["map"])
+    return dict(q=q, ksm=ksm, q8=q8, qs=qs, k8=k8, ks=ks, v8=v8, vs=vs, map=pr["map"], lut=lut.int(), valid=valid.int(), H=H)
+
+
+@pytest.mark.parametrize("gran", [2, 3])
+@pytest.mark.parametrize("N,D,causal", [(1500, 64, False), (1000, 128, False), (900, 128, True)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_per_warp_and_per_thread_scales_match_oracle(gran, N, D, causal, dtype):
+    """qk_quant_gran 2 and 3 (csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:106-136): the kernel applies one Q scale per
+    32 rows, or per-thread Q and K scales, exactly where the reference's accumulator layout puts them."""
+    from spargeattn_b200 import ops
+    c = _gran_case(N, D, dtype, 51, gran, causal=causal)
+    dev = lambda t: t.cuda().contiguous()
+    o = ops.attn_fwd(dev(c["q8"]), dev(c["k8"]), dev(O.e4m3_bits(c["v8"])), dev(c["lut"]), dev(c["valid"]), None,
+                     dev(c["qs"]), dev(c["ks"]), dev(c["vs"]), D ** -0.5, causal, dtype, qk_quant_gran=gran)
+    _status_ok()
+    ref, _ = O.attention_blockwise(c["q8"], c["qs"], c["k8"], c["ks"], c["v8"], c["vs"], c["map"], D ** -0.5, None,
+                                   token_causal=causal, out_dtype=dtype, pv_skip=False, qk_quant_gran=gran)
+    _check(o, ref)
+    # the finer scales must matter for this input: reading them with the per-block layout gives another result
+    if gran == 3:
+        wrong, _ = O.attention_blockwise(c["q8"], c["qs"][..., ::32].contiguous(), c["k8"], c["ks"][..., ::4].contiguous(),
+                                         c["v8"], c["vs"], c["map"], D ** -0.5, None, token_causal=causal,
+                                         out_dtype=dtype, pv_skip=False)
+        assert O.precision_metric(o.float().cpu(), wrong.float())["L1"] > 2e-2
+
+
+def test_per_warp_quantiser_is_bit_exact_and_feeds_granularity_two():
+    """per_warp_int8 (spas_sage_attn/quant_per_block.py:102-148): INT8 bytes and scales equal the oracle's, groups
+    past the end of the sequence get 1e-7, NHD is a view of the same result; its output runs through the kernel."""
+    from spargeattn_b200 import core, ops
+    B, H, N, D = 1, 2, 1100, 128
+    q, k, v = _inputs(B, H, N, D, torch.bfloat16, 52)
+    q8, qs, k8, ks = core.per_warp_int8(q.cuda(), k.cuda())
+    q8o, qso, k8o, kso = O.per_warp_int8(q, k)
+    assert qs.shape == (B, H, (N + 127) // 128 * 4, 1) and ks.shape == (B, H, (N + 63) // 64, 1)
+    assert torch.equal(q8.cpu(), q8o) and torch.equal(k8.cpu(), k8o)
+    assert torch.equal(qs.cpu().squeeze(-1), qso) and torch.equal(ks.cpu().squeeze(-1), kso)
+    assert float(qso[0, 0, -1]) == pytest.approx(1e-7) and (N + 31) // 32 < qso.shape[-1]
+    q8n, qsn, k8n, ksn = core.per_warp_int8(q.transpose(1, 2).contiguous().cuda(), k.transpose(1, 2).contiguous().cuda(),
+                                            tensor_layout="NHD")
+    assert q8n.shape == (B, N, H, D) and torch.equal(q8n.transpose(1, 2), q8) and torch.equal(qsn, qs)
+    with pytest.raises(ValueError):
+        core.per_warp_int8(q.cuda(), k.cuda(), tensor_layout="HDN")
+    with pytest.raises(ValueError):
+        ops.attn_fwd(q8, k8, k8.view(torch.uint8), torch.zeros(B, H, 9, 18, dtype=torch.int32, device="cuda"),
+                     torch.zeros(B, H, 9, dtype=torch.int32, device="cuda"), None, qs, ks,
+                     torch.ones(B, H, D, device="cuda"), 1.0, False, torch.bfloat16, qk_quant_gran=4)
+
+
+@pytest.mark.parametrize("gran", [1, 3])
+def test_per_warp_pv_threshold_mode_matches_oracle(gran):
+    """PVThresholdMode::kPerWarp: each 32-row group drops a block's P.V on its own. The output matches the oracle run
+    in that mode, the per-group counts match its counts (decisions at the threshold may differ by rounding: 1 %),
+    groups of one block differ from each other, and no group keeps fewer products than the per-block mode."""
+    from spargeattn_b200 import ops
+    N, D, dtype = 2048, 64, torch.bfloat16
+    c = _gran_case(N, D, dtype, 14, gran)
+    H = c["H"]
+    pv = O.hyperparameter_check(4.0, H)
+    dev = lambda t: t.cuda().contiguous()
+    args = (dev(c["q8"]), dev(c["k8"]), dev(O.e4m3_bits(c["v8"])), dev(c["lut"]), dev(c["valid"]))
+    scales = (dev(c["qs"]), dev(c["ks"]), dev(c["vs"]))
+    o2, cnt2 = ops.attn_fwd(*args, dev(pv), *scales, D ** -0.5, False, dtype, return_pv_count=True, qk_quant_gran=gran,
+                            pv_threshold_mode=2)
+    _status_ok()
+    o1, cnt1 = ops.attn_fwd(*args, dev(pv), *scales, D ** -0.5, False, dtype, return_pv_count=True, qk_quant_gran=gran,
+                            pv_threshold_mode=1)
+    o0, cnt0 = ops.attn_fwd(*args, dev(pv), *scales, D ** -0.5, False, dtype, return_pv_count=True, qk_quant_gran=gran,
+                            pv_threshold_mode=0)
+    _status_ok()
+    counts = torch.zeros(1, H, c["valid"].shape[-1] * 4, dtype=torch.int32)
+    ref, skipped = O.attention_blockwise(c["q8"], c["qs"], c["k8"], c["ks"], c["v8"], c["vs"], c["map"], D ** -0.5, pv,
+                                         out_dtype=dtype, qk_quant_gran=gran, pv_threshold_mode=2, group_counts=counts)
+    _check(o2, ref)
+    cnt2, cnt1, cnt0 = cnt2.cpu(), cnt1.cpu(), cnt0.cpu()
+    live4 = c["valid"].repeat_interleave(4, dim=-1)
+    assert torch.equal(cnt0, live4)                                       # mode 0 ignores the threshold
+    assert skipped > 0 and int((live4 - counts).sum()) == skipped
+    assert abs(int(cnt2.sum()) - int(counts.sum())) <= max(1, skipped // 100), (int(cnt2.sum()), int(counts.sum()))
+    assert (cnt2 != counts).float().mean().item() < 0.02
+    assert (cnt2 <= live4).all() and (cnt2 >= cnt1).all()                 # a group can only drop what its block may drop
+    per_block = cnt2.view(1, H, -1, 4)
+    assert (per_block != per_block[..., :1]).any()                        # the four groups of a block decide differently
+    assert int(cnt2.sum()) < int(cnt1.sum() * 0 + live4.sum())            # something was dropped
