@@ -23,25 +23,47 @@
 
 namespace sparge {
 
+// Packed helpers: two channels per 32-bit word in, two fp32 lanes out. Every arithmetic step below is the
+// per-lane IEEE operation of the scalar formulation (packed f32x2 instructions round each lane on its own),
+// so results are bit-identical to it while taking half the issue slots.
 template <typename T>
-__device__ __forceinline__ float unpack16(uint32_t w, int hi);
+__device__ __forceinline__ float2 unpack2(uint32_t w);
 template <>
-__device__ __forceinline__ float unpack16<__nv_bfloat16>(uint32_t w, int hi) {
-  return __uint_as_float(hi ? (w & 0xffff0000u) : (w << 16));
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
 template <>
-__device__ __forceinline__ float unpack16<__half>(uint32_t w, int hi) {
-  return __half2float(__ushort_as_half((unsigned short)(hi ? (w >> 16) : (w & 0xffffu))));
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
 template <typename T>
-__device__ __forceinline__ uint32_t bits16(float v);
+__device__ __forceinline__ uint32_t pack2_rn(float2 v);
 template <>
-__device__ __forceinline__ uint32_t bits16<__nv_bfloat16>(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ uint32_t pack2_rn<__nv_bfloat16>(float2 v) {
+  const __nv_bfloat162 h = __float22bfloat162_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 template <>
-__device__ __forceinline__ uint32_t bits16<__half>(float v) { return __half_as_ushort(__float2half_rn(v)); }
+__device__ __forceinline__ uint32_t pack2_rn<__half>(float2 v) {
+  const __half2 h = __float22half2_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// {sat8(hi), sat8(lo)} into the low half of the result, the low half of `upper` into its high half
+__device__ __forceinline__ uint32_t pack_s8x2(int hi, int lo, uint32_t upper) {
+  uint32_t d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+  return d;
+}
 
 // Thread layout: TPR = D/8 threads per row (8 channels each), G = BS/8 row groups; thread (g, cg)
-// owns rows 8g..8g+7 of channel group cg. blockDim = G * TPR (64 .. 256).
+// owns rows 8g..8g+7 of channel group cg. blockDim = G * TPR (32 .. 256).
+//
+// Row norms: every thread has a partial sum of squares for each of its 8 rows. The butterfly over the TPR
+// threads of a row is run as a reduce-scatter -- at the step with partner distance b a thread keeps the half of
+// its rows selected by that bit of its index and receives the partner's partials for them -- so the additions
+// are those of the plain butterfly (same partners, same order xor TPR/2 ... xor 1) but each row's total, its
+// square root and its reciprocal are computed once instead of by all TPR threads; the reciprocals then go back
+// to the row's threads with one shuffle per row.
 template <typename T, int D, int BS, bool HAS_KM, bool WANT_POOL>
 __global__ void __launch_bounds__((BS / 8) * (D / 8))
 pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float* __restrict__ simthr,
@@ -62,12 +84,15 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
   const int rows_here = max(0, min(BS, N - row_base));   // 0: a 32-row group past the end (scale 1e-7, nothing else)
   const T* xb = x + (size_t)(bh / H) * sb + (size_t)(bh % H) * sh + (size_t)row_base * sn;
 
-  float kmv[8];
+  float2 kmv[4];
   if (HAS_KM) {
     const uint4 p = *reinterpret_cast<const uint4*>(km + (size_t)bh * D + cg * 8);
     const uint32_t w[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
-    for (int i = 0; i < 8; i++) kmv[i] = unpack16<T>(w[i >> 1], i & 1);
+    for (int c = 0; c < 4; c++) {
+      kmv[c] = unpack2<T>(w[c]);
+      kmv[c] = make_float2(-kmv[c].x, -kmv[c].y);          // x - m is evaluated as x + (-m): the same rounding
+    }
   }
 
   // ---- load the thread's 8 rows (all loads in flight before the first use)
@@ -78,54 +103,77 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
     raw[i] = (row < rows_here) ? *reinterpret_cast<const uint4*>(xb + (size_t)row * sn + cg * 8) : make_uint4(0, 0, 0, 0);
   }
 
+  // ---- pass 1: mean subtraction in the 16-bit type, amax, pooled sums, partial sums of squares
   float amax = 0.f;
-  float pacc[8], hacc[8];
+  float2 pacc[4];
+  float ss[8];
 #pragma unroll
-  for (int c = 0; c < 8; c++) { pacc[c] = 0.f; hacc[c] = 0.f; }
-  int zero_row = 0;
-
+  for (int c = 0; c < 4; c++) pacc[c] = make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < 8; i++) {
-    const bool valid = (g * 8 + i) < rows_here;
     uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-    float v[8];
+    float2 v[4];
 #pragma unroll
-    for (int c = 0; c < 8; c++) v[c] = unpack16<T>(w[c >> 1], c & 1);
+    for (int c = 0; c < 4; c++) v[c] = unpack2<T>(w[c]);
     if (HAS_KM) {
-      if (valid) {
+      if ((g * 8 + i) < rows_here) {   // padded rows stay zero
 #pragma unroll
-        for (int c = 0; c < 8; c += 2) {   // subtraction rounded to the 16-bit type; keep the rounded bits
-          const uint32_t lo = bits16<T>(__fsub_rn(v[c], kmv[c])), hi = bits16<T>(__fsub_rn(v[c + 1], kmv[c + 1]));
-          w[c >> 1] = lo | (hi << 16);
+        for (int c = 0; c < 4; c++) {   // subtraction rounded to the 16-bit type; keep the rounded bits
+          w[c] = pack2_rn<T>(__fadd2_rn(v[c], kmv[c]));
+          v[c] = unpack2<T>(w[c]);
         }
         raw[i] = make_uint4(w[0], w[1], w[2], w[3]);
-#pragma unroll
-        for (int c = 0; c < 8; c++) v[c] = unpack16<T>(w[c >> 1], c & 1);
       }
     }
-    amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
-                             fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7])))));
+    amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(v[0].x), fabsf(v[0].y)), fmaxf(fabsf(v[1].x), fabsf(v[1].y))),
+                             fmaxf(fmaxf(fabsf(v[2].x), fabsf(v[2].y)), fmaxf(fabsf(v[3].x), fabsf(v[3].y)))));
     if (WANT_POOL) {
-      float ss = 0.f;
+      float q = 0.f;
 #pragma unroll
-      for (int c = 0; c < 8; c++) {
-        pacc[c] = __fadd_rn(pacc[c], v[c]);
-        ss = __fmaf_rn(v[c], v[c], ss);
+      for (int c = 0; c < 4; c++) {
+        pacc[c] = __fadd2_rn(pacc[c], v[c]);
+        q = __fmaf_rn(v[c].x, v[c].x, q);                  // one chain over the 8 channels in ascending order
+        q = __fmaf_rn(v[c].y, v[c].y, q);
       }
+      ss[i] = q;
+    }
+  }
+
+  // ---- row norms -> reciprocals, one row per thread (see the header)
+  float rinv[8];
+  int zero_row = 0;
+  if (WANT_POOL) {
+    float vals[8];
 #pragma unroll
-      for (int o = TPR / 2; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
-      const float nrm = __fsqrt_rn(ss);
-      if (valid) {
-        if (nrm == 0.f) {
-          zero_row = 1;
-        } else {
-          const float rinv = __fdiv_rn(1.0f, nrm);
+    for (int i = 0; i < 8; i++) vals[i] = ss[i];
+    int n = 8;
 #pragma unroll
-          for (int c = 0; c < 8; c++)
-            hacc[c] = __fadd_rn(hacc[c], __half2float(__float2half_rn(__fmul_rn(v[c], rinv))));
+    for (int b = TPR / 2; b > 0; b >>= 1) {
+      if (n > 1) {
+        const bool upper = (cg & b) != 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          if (j < n / 2) {
+            const float keep = upper ? vals[n / 2 + j] : vals[j];
+            const float send = upper ? vals[j] : vals[n / 2 + j];
+            vals[j] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, b));
+          }
         }
+        n >>= 1;
+      } else {
+        vals[0] = __fadd_rn(vals[0], __shfl_xor_sync(0xffffffffu, vals[0], b));
       }
     }
+    // this thread now holds the total of row `mine` of its group's 8 rows
+    const int mine = TPR == 16 ? (cg >> 1) : cg;
+    const float nrm = __fsqrt_rn(vals[0]);
+    const bool live = (g * 8 + mine) < rows_here;
+    float r = 0.f;                                          // padded and all-zero rows add zeros to the unit-vector sum
+    if (live && nrm == 0.f) zero_row = 1;
+    if (live && nrm != 0.f) r = __fdiv_rn(1.0f, nrm);
+    const int group_lane0 = lane & ~(TPR - 1);
+#pragma unroll
+    for (int i = 0; i < 8; i++) rinv[i] = __shfl_sync(0xffffffffu, r, group_lane0 + (TPR == 16 ? 2 * i : i));
   }
 
   // ---- block amax -> scale
@@ -133,9 +181,9 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
   if (lane == 0) s_amax[warp] = amax;
   if (WANT_POOL) {
 #pragma unroll
-    for (int c = 0; c < 8; c++) {
-      s_part[0][g][cg * 8 + c] = pacc[c];
-      s_part[WANT_POOL ? 1 : 0][g][cg * 8 + c] = hacc[c];
+    for (int c = 0; c < 4; c++) {
+      s_part[0][g][cg * 8 + 2 * c] = pacc[c].x;
+      s_part[0][g][cg * 8 + 2 * c + 1] = pacc[c].y;
     }
   }
   const int any_zero = __syncthreads_or(zero_row);
@@ -146,36 +194,55 @@ pool_quant_kernel(const T* __restrict__ x, const T* __restrict__ km, const float
   const float rs = __fdiv_rn(1.0f, scale);
   if (tid == 0) scale_out[(size_t)bh * nb + blk] = scale;
 
-  // ---- quantise from registers
+  // ---- pass 2 from registers: unit vectors (fp16-rounded) summed per channel, INT8 quantisation
+  const float2 rs2 = make_float2(rs, rs), nscale2 = make_float2(-scale, -scale);
+  float2 hacc[4];
+#pragma unroll
+  for (int c = 0; c < 4; c++) hacc[c] = make_float2(0.f, 0.f);
   int8_t* qb = xq + ((size_t)bh * N + row_base) * D;
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const int row = g * 8 + i;
-    if (row < rows_here) {
-      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-      uint32_t out[2] = {0u, 0u};
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+    int q[8];
 #pragma unroll
-      for (int c = 0; c < 8; c++) {
-        const float xv = unpack16<T>(w[c >> 1], c & 1);
-        const float y0 = __fmul_rn(xv, rs);
-        const float e = __fmaf_rn(-scale, y0, xv);
-        float y = __fmaf_rn(e, rs, y0);                      // == RN(xv / scale)
-        y = __fadd_rn(y, y >= 0.f ? 0.5f : -0.5f);
-        const int q = (int)y;                                // truncation toward zero
-        out[c >> 2] |= (uint32_t)(q & 0xff) << ((c & 3) * 8);
+    for (int c = 0; c < 4; c++) {
+      const float2 xv = unpack2<T>(w[c]);
+      if (WANT_POOL) {
+        const float2 u = __fmul2_rn(xv, make_float2(rinv[i], rinv[i]));
+        hacc[c] = __fadd2_rn(hacc[c], __half22float2(__float22half2_rn(u)));
       }
-      *reinterpret_cast<uint2*>(qb + (size_t)row * D + cg * 8) = make_uint2(out[0], out[1]);
+      const float2 y0 = __fmul2_rn(xv, rs2);
+      const float2 e = __ffma2_rn(nscale2, y0, xv);        // exact remainder
+      float2 y = __ffma2_rn(e, rs2, y0);                   // == RN(xv / scale) per lane
+      // + 0.5 with the sign of y, then truncation toward zero (y = -0 gives 0 either way)
+      const float2 hlf = make_float2(__uint_as_float((__float_as_uint(y.x) & 0x80000000u) | 0x3f000000u),
+                                     __uint_as_float((__float_as_uint(y.y) & 0x80000000u) | 0x3f000000u));
+      y = __fadd2_rn(y, hlf);
+      q[2 * c] = (int)y.x;
+      q[2 * c + 1] = (int)y.y;
+    }
+    if (row < rows_here) {
+      const uint32_t lo = pack_s8x2(q[1], q[0], pack_s8x2(q[3], q[2], 0u));
+      const uint32_t hi = pack_s8x2(q[5], q[4], pack_s8x2(q[7], q[6], 0u));
+      *reinterpret_cast<uint2*>(qb + (size_t)row * D + cg * 8) = make_uint2(lo, hi);
     }
   }
 
   if (WANT_POOL) {
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      s_part[1][g][cg * 8 + 2 * c] = hacc[c].x;
+      s_part[1][g][cg * 8 + 2 * c + 1] = hacc[c].y;
+    }
+    __syncthreads();
     double sq = 0.0;
     if (tid < D) {
       double ps = 0.0, hs = 0.0;
 #pragma unroll
       for (int r = 0; r < G; r++) {
         ps += (double)s_part[0][r][tid];
-        hs += (double)s_part[WANT_POOL ? 1 : 0][r][tid];
+        hs += (double)s_part[1][r][tid];
       }
       pool[((size_t)bh * nb + blk) * D + tid] = Elem<T>::from_float(__fdiv_rn((float)ps, (float)rows_here));
       sq = hs * hs;

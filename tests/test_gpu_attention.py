@@ -343,7 +343,8 @@ def test_per_warp_quantiser_is_bit_exact_and_feeds_granularity_two():
 def test_per_warp_pv_threshold_mode_matches_oracle(gran):
     """PVThresholdMode::kPerWarp: each 32-row group drops a block's P.V on its own. The output matches the oracle run
     in that mode, the per-group counts match its counts (decisions at the threshold may differ by rounding: 1 %),
-    groups of one block differ from each other, and no group keeps fewer products than the per-block mode."""
+    groups of one block differ from each other, and no group keeps more products than the per-block mode (which
+    drops a block only when all four groups would)."""
     from spargeattn_b200 import ops
     N, D, dtype = 2048, 64, torch.bfloat16
     c = _gran_case(N, D, dtype, 14, gran)
@@ -370,7 +371,7 @@ def test_per_warp_pv_threshold_mode_matches_oracle(gran):
     assert skipped > 0 and int((live4 - counts).sum()) == skipped
     assert abs(int(cnt2.sum()) - int(counts.sum())) <= max(1, skipped // 100), (int(cnt2.sum()), int(counts.sum()))
     assert (cnt2 != counts).float().mean().item() < 0.02
-    assert (cnt2 <= live4).all() and (cnt2 >= cnt1).all()                 # a group can only drop what its block may drop
+    assert (cnt2 <= cnt1).all() and (cnt1 <= live4).all()                 # the block drops only what every group drops
     per_block = cnt2.view(1, H, -1, 4)
     assert (per_block != per_block[..., :1]).any()                        # the four groups of a block decide differently
-    assert int(cnt2.sum()) < int(cnt1.sum() * 0 + live4.sum())            # something was dropped
+    assert int(cnt2.sum()) < int(cnt1.sum()) < int(live4.sum())           # both modes dropped something, per-warp more
