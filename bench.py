@@ -385,21 +385,14 @@ def main():
     # ---- end-to-end arm: pinned host buffers in, host buffer out, copies inside the timed region
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty_like(hq).pin_memory()
-    if whole:
-        # the library's host-buffer front end: head chunks pipelined over upload / compute / download streams
-        from spargeattn_b200.host import spas_sage2_attn_meansim_topk_host
+    # the library's host-buffer front end: head chunks pipelined over upload / compute / download streams; a rank
+    # that owns part of a head moves only its query rows and its rows of the result
+    from spargeattn_b200.host import spas_sage2_attn_meansim_topk_host
 
-        def e2e_step():
-            spas_sage2_attn_meansim_topk_host(hq, hk, hv, out=ho, device=dev, heads_per_chunk=args.e2e_heads_per_chunk,
-                                              topk=topk, is_causal=causal, pvthreshd=args.pvthreshd)
-    else:
-        dq, dk, dv = (torch.empty_like(t) for t in (q, k, v))
-
-        def e2e_step():
-            dq.copy_(hq, non_blocking=True)
-            dk.copy_(hk, non_blocking=True)
-            dv.copy_(hv, non_blocking=True)
-            ho.copy_(api(dq, dk, dv), non_blocking=True)
+    def e2e_step():
+        spas_sage2_attn_meansim_topk_host(hq, hk, hv, out=ho, device=dev, units=None if whole else units,
+                                          heads_per_chunk=args.e2e_heads_per_chunk if whole else 1,
+                                          topk=topk, is_causal=causal, pvthreshd=args.pvthreshd)
 
     for _ in range(3):
         e2e_step()
@@ -407,7 +400,8 @@ def main():
     ms_e2e = timed(e2e_step, e2e_steps)
     clk.__exit__()
     e2e_value = total_ops / (ms_e2e * 1e-3) / 1e12
-    in_bytes, out_bytes = 3 * q.numel() * 2, q.numel() * 2
+    own_rows = sum(min((a + n) * 128, N) - a * 128 for (_, _, a, n) in units)      # query rows this rank owns
+    in_bytes, out_bytes = (own_rows + 2 * len(units) * N) * D * 2, own_rows * D * 2    # owned q rows + whole k, v / owned o rows
     if dist is not None:       # bytes of the whole job per step
         t = torch.tensor([float(in_bytes), float(out_bytes)], device=dev)
         dist.all_reduce(t)

@@ -176,6 +176,36 @@ def test_host_front_end_matches_device_call():
     _status_ok()
 
 
+def test_host_front_end_with_partially_owned_heads():
+    """Row-sharded host entry point: a rank's units (whole heads and parts of heads) give, on the rows it owns, the
+    bytes of the full call; rows it does not own are neither read from q nor written to the result."""
+    import spargeattn_b200 as S
+    from spargeattn_b200.host import spas_sage2_attn_meansim_topk_host
+    from spargeattn_b200.sharding import partition_rows
+    B, H, N, D = 1, 3, 1500, 128
+    q, k, v = _inputs(B, H, N, D, torch.bfloat16, 19)
+    ref = S.spas_sage2_attn_meansim_topk_cuda(q.cuda(), k.cuda(), v.cuda(), topk=0.5).cpu()
+    nq = (N + 127) // 128
+    seen = torch.zeros(H, N, dtype=torch.bool)
+    for units in partition_rows(B, H, nq, 4):
+        heads = [h for (_, h, _, _) in units]
+        hq, hk, hv = (t[:, heads].contiguous().pin_memory() for t in (q, k, v))
+        for i, (_, _, a, n) in enumerate(units):           # rows of q outside the unit must not matter
+            hq[0, i, :a * 128] = float("nan")
+            hq[0, i, (a + n) * 128:] = float("nan")
+        out = torch.full((1, len(units), N, D), -7.0, dtype=torch.bfloat16).pin_memory()
+        for hpc in (1, 2):
+            spas_sage2_attn_meansim_topk_host(hq, hk, hv, out=out, units=units, heads_per_chunk=hpc, topk=0.5)
+            torch.cuda.synchronize()
+            for i, (_, h, a, n) in enumerate(units):
+                r0, r1 = a * 128, min((a + n) * 128, N)
+                assert torch.equal(out[0, i, r0:r1], ref[0, h, r0:r1])
+                assert (out[0, i, :r0] == -7.0).all() and (out[0, i, r1:] == -7.0).all()
+                seen[h, r0:r1] = True
+    assert seen.all()
+    _status_ok()
+
+
 @pytest.mark.parametrize("N", [128, 129, 191, 257])
 def test_tiny_and_ragged_lengths(N):
     import spargeattn_b200 as S
