@@ -195,8 +195,9 @@ int sparge_attn_fwd_gran(const int8_t* q_int8, const int8_t* k_int8, const uint8
                          int32_t* pv_count, const int32_t* q_block_ranges, int q_blocks_max, int qk_quant_gran,
                          int pv_threshold_mode, sparge_stream_t stream);
 
-/* Failure-detection self test: launches one warp that waits on a barrier nobody signals, bounded by
- * slices x slice_ns nanoseconds (at most 0.1 s in total), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into
+/* Failure-detection self test: launches one warp that waits on a barrier nobody signals, for `slices` tries with
+ * the suspend hint slice_ns (a try lasts about 4 us on a B200 whatever the hint; slices x max(slice_ns, 4000) may
+ * not exceed 0.1 s), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into
  * *dev_status when the bounded wait gives up -- the same code path that sparge_attn_fwd takes if a
  * producer / MMA / softmax hand-off ever stalls. The kernel then exits normally; the context stays usable.
  * The reference has no counterpart (its sm90 kernel spins without a limit, qk_int_sv_f8_cuda_sm90.cuh:117-132). */

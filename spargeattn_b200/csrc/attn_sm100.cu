@@ -708,7 +708,9 @@ __global__ void wait_expiry_selftest_kernel(int32_t* dev_status, uint32_t slice_
 extern "C" int sparge_selftest_wait_expiry(int32_t* dev_status, unsigned int slice_ns, unsigned int slices,
                                            sparge_stream_t stream) {
   if (!dev_status) return SPARGE_ERR_NULL;
-  if (slice_ns == 0 || slices == 0 || (unsigned long long)slice_ns * slices > 100000000ull) return SPARGE_ERR_INVALID_ARG;
+  // a try lasts about 4 us even with a smaller hint: the test may not wait longer than 0.1 s either way
+  if (slice_ns == 0 || slices == 0 || (unsigned long long)std::max(slice_ns, 4000u) * slices > 100000000ull)
+    return SPARGE_ERR_INVALID_ARG;
   sparge::wait_expiry_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(dev_status, slice_ns, slices);
   return sparge::launch_status();
 }

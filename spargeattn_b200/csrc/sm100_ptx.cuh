@@ -2,17 +2,13 @@
 // mbarriers with bounded waits, TMA tiled loads, tensor-memory (TMEM) allocation,
 // tcgen05.mma / commit / ld / st, and the shared-memory + instruction descriptors they take.
 //
-// Every spin in this file is bounded: a wait that does not complete within
-// SPARGE_WAIT_LIMIT_CYCLES returns false, and the caller records a status word and unwinds.
+// Every spin in this file is bounded: a wait that does not complete within kWaitSlices tries (about one
+// second) returns false, and the caller records a status word and unwinds.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
 
 namespace sparge {
-
-#ifndef SPARGE_WAIT_LIMIT_CYCLES
-#define SPARGE_WAIT_LIMIT_CYCLES (2000000000ll)   // about one second at B200 clocks
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -54,11 +50,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. Returns false when the phase did not complete in time.
-// Each try_wait may suspend the thread for up to kWaitSliceNs (it resumes as soon as the phase
-// completes), so a waiting role costs a handful of instructions per slice instead of a hot spin;
-// kWaitSlices slices bound the total wait to about one second.
-constexpr uint32_t kWaitSliceNs = 1000000u;   // 1 ms
-constexpr uint32_t kWaitSlices = 1000u;
+// Each try_wait suspends the thread until the phase completes or the hardware's own time limit runs out,
+// so a waiting role costs a handful of instructions per try instead of a hot spin. Measured on a B200: a
+// try that does not succeed returns after about 4 us whatever hint it is given (2 000 tries on a barrier
+// nobody signals take 8.05 ms with a 10 ns and with a 1 us hint). The hint is set to that figure and the
+// number of tries bounds a wait to about one second -- far above any wait of a healthy run (microseconds)
+// and above a time slice lost to another process on a shared GPU.
+constexpr uint32_t kWaitSliceNs = 4000u;
+constexpr uint32_t kWaitSlices = 250000u;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t slice_ns = kWaitSliceNs,
                                           uint32_t slices = kWaitSlices) {
   uint32_t ok;
