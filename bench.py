@@ -51,6 +51,9 @@ def parse():
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads, comparators and the reference-on-GPU leg")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=2)
     ap.add_argument("--quick", action="store_true", help="device-resident arm only (for profiler runs)")
+    ap.add_argument("--share", default=None, metavar="R/W",
+                    help="single process: run the share that rank R of a W-GPU job would own (the row sharding has no "
+                         "collective, so one GPU can time any rank's share); the printed value assumes every rank takes as long")
     return ap.parse_args()
 
 
@@ -325,7 +328,12 @@ def main():
     # ---- this rank's share: contiguous runs of (batch, head, query block) cells of equal expected cost
     n_sel = max(1, int(topk * ((N + 63) // 64)))
     row_cost = [min(n_sel, 2 * (i + 1)) for i in range(nq)] if causal else None
-    units = sharding.partition_rows(B, H, nq, world, row_cost)[rank]
+    part_rank, part_world = rank, world
+    if args.share:
+        assert world == 1, "--share is for a single process"
+        part_rank, part_world = (int(x) for x in args.share.split("/"))
+        assert 0 <= part_rank < part_world
+    units = sharding.partition_rows(B, H, nq, part_world, row_cost)[part_rank]
     heads = [(b, h) for (b, h, _, _) in units]
     q, k, v = syn.workload_heads_qkv(idx, heads, dev)                  # [1, Hloc, N, D]
     whole = all(a == 0 and n == nq for (_, _, a, n) in units)
@@ -369,8 +377,8 @@ def main():
     total_ops = dense_equiv_ops(B, H, N, D, causal)
     value = total_ops / (ms_step * 1e-3) / 1e12
     config = {"workload": workload_text(syn, idx, topk, args.pvthreshd),
-              "sharding": (f"strong scaling over {world} GPU(s): (batch, head, query-block) cells cut into {world} contiguous "
-                           f"runs of equal cost, no collective; rank 0 owns {[list(u) for u in units]} as (b, h, first block, blocks)"),
+              "sharding": (f"strong scaling over {part_world} GPU(s): (batch, head, query-block) cells cut into {part_world} contiguous "
+                           f"runs of equal cost, no collective; rank {part_rank} owns {[list(u) for u in units]} as (b, h, first block, blocks)"),
               "l2_policy": "inputs larger than L2 on every rank (q,k,v = %.0f MB on rank 0; L2 126 MB)" % (3 * q.numel() * 2 / 1e6)}
 
     if args.quick:
@@ -497,6 +505,8 @@ def main():
                         "d2h_bytes_per_step": out_bytes, "numa_node_bound": numa},
                 "gpu_launches": 9 * args.steps * world, "roofline": roofline, "kernels": kernels,
                 "cpu_baseline": cpu_baseline}
+        if args.share:
+            line["share_of"] = args.share
         line.update(extras)
         print(json.dumps(line))
     if dist is not None:
