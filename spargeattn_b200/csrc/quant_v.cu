@@ -51,7 +51,20 @@ __global__ void __launch_bounds__(256) v_amax_kernel(const T* __restrict__ v, un
   float mx[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) mx[i] = 0.f;
-  for (int row = row_begin + r0; row < row_end; row += RPP) {
+#ifndef VQ_UNROLL
+#define VQ_UNROLL 4
+#endif
+  int row = row_begin + r0;
+  for (; row + (VQ_UNROLL - 1) * RPP < row_end; row += VQ_UNROLL * RPP) {   // several 128-bit loads in flight per thread
+    Pack8<T> p[VQ_UNROLL];
+#pragma unroll
+    for (int u = 0; u < VQ_UNROLL; u++) p[u] = *reinterpret_cast<const Pack8<T>*>(base + (size_t)(row + u * RPP) * sn + cg * 8);
+#pragma unroll
+    for (int u = 0; u < VQ_UNROLL; u++)
+#pragma unroll
+      for (int i = 0; i < 8; i++) mx[i] = fmaxf(mx[i], fabsf(to_f16_value<T>(p[u].v[i])));
+  }
+  for (; row < row_end; row += RPP) {
     Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * sn + cg * 8);
 #pragma unroll
     for (int i = 0; i < 8; i++) mx[i] = fmaxf(mx[i], fabsf(to_f16_value<T>(p.v[i])));
@@ -84,16 +97,24 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const T* __restrict__ v, c
   }
   const T* base = v + (size_t)(bh / H) * sb + (size_t)(bh % H) * sh;
   uint8_t* out = v8 + (size_t)bh * N_pad * D;
-  for (int row = row_begin + r0; row < row_end; row += RPP) {
-    uint2 w = make_uint2(0u, 0u);
-    if (row < N) {
-      Pack8<T> p = *reinterpret_cast<const Pack8<T>*>(base + (size_t)row * sn + cg * 8);
-      float f[8];
+  auto quantise = [&](const Pack8<T>& p) {
+    float f[8];
 #pragma unroll
-      for (int i = 0; i < 8; i++) f[i] = __fmul_rn(to_f16_value<T>(p.v[i]), r[i]);
-      w.x = cvt_e4m3x4(f[0], f[1], f[2], f[3]);
-      w.y = cvt_e4m3x4(f[4], f[5], f[6], f[7]);
-    }
+    for (int i = 0; i < 8; i++) f[i] = __fmul_rn(to_f16_value<T>(p.v[i]), r[i]);
+    return make_uint2(cvt_e4m3x4(f[0], f[1], f[2], f[3]), cvt_e4m3x4(f[4], f[5], f[6], f[7]));
+  };
+  int row = row_begin + r0;
+  const int full_end = min(row_end, N);                  // rows below N hold data, the rest of the pad is zeros
+  for (; row + (VQ_UNROLL - 1) * RPP < full_end; row += VQ_UNROLL * RPP) {
+    Pack8<T> p[VQ_UNROLL];
+#pragma unroll
+    for (int u = 0; u < VQ_UNROLL; u++) p[u] = *reinterpret_cast<const Pack8<T>*>(base + (size_t)(row + u * RPP) * sn + cg * 8);
+#pragma unroll
+    for (int u = 0; u < VQ_UNROLL; u++) *reinterpret_cast<uint2*>(out + (size_t)(row + u * RPP) * D + cg * 8) = quantise(p[u]);
+  }
+  for (; row < row_end; row += RPP) {
+    uint2 w = make_uint2(0u, 0u);
+    if (row < N) w = quantise(*reinterpret_cast<const Pack8<T>*>(base + (size_t)row * sn + cg * 8));
     *reinterpret_cast<uint2*>(out + (size_t)row * D + cg * 8) = w;
   }
 }
