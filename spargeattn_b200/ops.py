@@ -2,6 +2,7 @@
 current CUDA stream.  These mirror the helper functions of the reference's
 spas_sage_attn/utils.py (get_pool_sim_triton_simmean_fuse_quant :270-280, get_quant :255-263,
 block_map_lut_triton :76-87) and the `_fused` / `_qattn` extension calls in core.py:143-158."""
+import threading
 from typing import Optional, Tuple
 
 import torch
@@ -24,8 +25,31 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_launch = threading.local()
+
+
 def _stream(t: torch.Tensor):
-    return torch.cuda.current_stream(t.device).cuda_stream
+    s = getattr(_launch, "stream", None)
+    return (s if s is not None else torch.cuda.current_stream(t.device)).cuda_stream
+
+
+class launch_on:
+    """Within this context the wrappers of this module launch their kernels on `stream` while their outputs are
+    still allocated from the current stream's pool: the caller orders `stream` after the current stream before
+    and the current stream after `stream` behind the block, so the tensors live and die like any other tensor
+    of the current stream (no cross-stream bookkeeping in the allocator)."""
+
+    def __init__(self, stream):
+        self.stream = stream
+
+    def __enter__(self):
+        self.prev = getattr(_launch, "stream", None)
+        _launch.stream = self.stream
+        return self
+
+    def __exit__(self, *exc):
+        _launch.stream = self.prev
+        return False
 
 
 def _need_cuda(*ts):

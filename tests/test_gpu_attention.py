@@ -176,6 +176,34 @@ def test_host_front_end_matches_device_call():
     _status_ok()
 
 
+def test_concurrent_preparation_gives_the_same_bytes():
+    """Mid-sized calls run Q pooling and the V quantiser on side streams beside the K chain: same bytes as the
+    one-stream order, also when calls follow each other on different streams."""
+    import spargeattn_b200 as S
+    from spargeattn_b200 import core
+    B, H, N, D = 1, 2, 3000, 128
+    q, k, v = (t.cuda() for t in _inputs(B, H, N, D, torch.bfloat16, 20))
+    lo, hi = core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS
+    try:
+        core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS = 1 << 40, 0          # one stream
+        ref = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5)
+        ref_c = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5, is_causal=True, pvthreshd=4.0)
+        core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS = 0, 1 << 40          # side streams
+        outs = []
+        other = torch.cuda.Stream()
+        for i in range(6):
+            with torch.cuda.stream(other if i % 2 else torch.cuda.current_stream()):
+                if i % 2:
+                    other.wait_stream(torch.cuda.default_stream())
+                outs.append(S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5))
+        out_c = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5, is_causal=True, pvthreshd=4.0)
+        torch.cuda.synchronize()
+    finally:
+        core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS = lo, hi
+    _status_ok()
+    assert all(torch.equal(o, ref) for o in outs) and torch.equal(out_c, ref_c)
+
+
 def test_host_front_end_with_partially_owned_heads():
     """Row-sharded host entry point: a rank's units (whole heads and parts of heads) give, on the rows it owns, the
     bytes of the full call; rows it does not own are neither read from q nor written to the result."""
