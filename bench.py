@@ -277,22 +277,51 @@ def reference_on_gpu(workloads):
         return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
 
+def _cpu_list(text):
+    cpus = []
+    for part in text.strip().split(","):
+        a, _, b = part.partition("-")
+        cpus += list(range(int(a), int(b or a) + 1))
+    return cpus
+
+
 def bind_to_gpu_numa_node(local):
-    """Pin this process (and the pinned host buffers it allocates afterwards) to the CPU cores of the GPU's NUMA node."""
+    """Pin this process (and the pinned host buffers it allocates afterwards: pages are placed on first touch) to the
+    CPU cores next to the GPU. The cores come from sysfs (the PCI device's NUMA node) or, where a container hides
+    that, from the CPU-affinity column of `nvidia-smi topo -m`. Returns what was done, or None."""
+    allowed = os.sched_getaffinity(0)
+
+    def bind(cpus, how):
+        cpus = set(cpus) & allowed
+        if not cpus or cpus == allowed:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return f"{len(cpus)} cpus ({how})"
+
     try:
         p = torch.cuda.get_device_properties(local)
         bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
         node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
-        if node < 0:
-            return None
-        cpus = []
-        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
-            a, _, b = part.partition("-")
-            cpus += list(range(int(a), int(b or a) + 1))
-        os.sched_setaffinity(0, set(cpus))
-        return node
+        if node >= 0:
+            done = bind(_cpu_list(open(f"/sys/devices/system/node/node{node}/cpulist").read()), f"sysfs numa node {node}")
+            if done:
+                return done
     except Exception:
-        return None
+        pass
+    try:
+        out = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout
+        rows = [[c.strip() for c in line.split("\t")] for line in out.splitlines() if line.strip()]
+        header = next(r for r in rows if "CPU Affinity" in r)
+        col = header.index("CPU Affinity")
+        # data rows carry the row label in front, so their columns are shifted by one against a header that starts
+        # with an empty cell; take the cell that parses as a cpu list at or next to the header's position
+        row = next(r for r in rows if r and r[0] == f"GPU{local}")
+        for c in (col, col + 1, col - 1):
+            if 0 <= c < len(row) and row[c] and all(ch.isdigit() or ch in ",-" for ch in row[c]):
+                return bind(_cpu_list(row[c]), "nvidia-smi topo")
+    except Exception:
+        pass
+    return None
 
 
 # ------------------------------------------------------------------------------------------ GPU arm
