@@ -87,8 +87,14 @@ __global__ void __launch_bounds__(256) v_quant_kernel(const T* __restrict__ v, c
                                                       long long sb, long long sh, long long sn) {
   constexpr int TPR = D / 8, RPP = 256 / TPR;
   const int tid = threadIdx.x, cg = tid % TPR, r0 = tid / TPR;
-  const int bh = blockIdx.y;
-  const int row_begin = blockIdx.x * kVRowsPerCta, row_end = min(N_pad, row_begin + kVRowsPerCta);
+#ifndef VQ_REVERSE
+#define VQ_REVERSE 1
+#endif
+  // The amax pass has just read V front to back; this pass walks it back to front, so that it starts with the
+  // rows that are still in L2 (a tensor larger than the cache would be re-read from DRAM in full either way).
+  const int bh = VQ_REVERSE ? gridDim.y - 1 - blockIdx.y : blockIdx.y;
+  const int chunk = VQ_REVERSE ? gridDim.x - 1 - blockIdx.x : blockIdx.x;
+  const int row_begin = chunk * kVRowsPerCta, row_end = min(N_pad, row_begin + kVRowsPerCta);
   float r[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) {
