@@ -468,6 +468,11 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
                 qf = q8[b, h, r0:r1].float()
                 rows = r1 - r0
                 m = torch.full((rows,), MASK_VALUE, dtype=torch.float32)
+                # Rows of a partial last query block beyond N: the reference's Q tile holds zeros there, their scores are
+                # zero, and they take part in the skip test's maximum over the block (update_mo has no row mask,
+                # attn_utils.cuh:418-466): after the first block their running maximum is 0 and their difference 0, so a
+                # partial query block never skips with a positive threshold.  m_pad is that running maximum.
+                m_pad = MASK_VALUE
                 d = torch.ones(rows, dtype=torch.float32)
                 acc = torch.zeros(rows, D, dtype=torch.float32)
                 live = torch.nonzero(block_map[b, h, i]).flatten().tolist()
@@ -484,15 +489,20 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
                     m_new = torch.maximum(m, rowmax)
                     is_tail = n_it >= len(live) - 2                    # last two live blocks never skip
                     keep = torch.ones(rows, dtype=torch.bool)
+                    pad_delta = (0.0 - m_pad) if rows < BLKQ else float("-inf")
+                    m_pad = max(m_pad, 0.0)
                     if pv_skip and not is_tail:
                         if pv_threshold_mode == 1:
-                            delta = (rowmax - m).max().item()
+                            delta = max((rowmax - m).max().item(), pad_delta)
                             if delta + float(pvthreshd[h]) <= 0:
                                 skipped += 1
                                 continue
                         else:                                          # each 32-row group on its own
                             for g0 in range(0, rows, 32):
-                                if (rowmax - m)[g0:g0 + 32].max().item() + float(pvthreshd[h]) <= 0:
+                                g_delta = (rowmax - m)[g0:g0 + 32].max().item()
+                                if g0 + 32 > rows:                     # the group that also holds padded rows
+                                    g_delta = max(g_delta, pad_delta)
+                                if g_delta + float(pvthreshd[h]) <= 0:
                                     keep[g0:g0 + 32] = False
                                     skipped += 1
                     if group_counts is not None:
@@ -561,7 +571,8 @@ def attention_blockwise_sampled(q8, q_scale, k8, k_scale, v8, v_scale, block_map
         m_new = torch.maximum(m, rowmax)
         upd = act.clone()
         if pv_skip:
-            delta = torch.where(row_ok, rowmax - m, torch.full_like(m, float("-inf"))).amax(dim=-1)
+            # padded rows of a partial last query block (zero Q rows, zero scores) take part, as in the reference
+            delta = (rowmax - m).amax(dim=-1)
             skip = act & (n_it < cnt - 2) & (delta + thr <= 0)
             skipped += int(skip.sum())
             upd = upd & ~skip

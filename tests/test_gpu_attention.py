@@ -433,3 +433,33 @@ def test_per_warp_pv_threshold_mode_matches_oracle(gran):
     per_block = cnt2.view(1, H, -1, 4)
     assert (per_block != per_block[..., :1]).any()                        # the four groups of a block decide differently
     assert int(cnt2.sum()) < int(cnt1.sum()) < int(live4.sum())           # both modes dropped something, per-warp more
+
+
+def test_partial_last_query_block_never_skips():
+    """The reference's skip test takes its maximum over all 128 rows of the Q tile, padded rows included (zero
+    scores, running maximum 0, difference 0: attn_utils.cuh:418-466 has no row mask), so a partial last query block
+    keeps every product while full blocks of the same head drop some. Kernel and oracle both reproduce that."""
+    from spargeattn_b200 import ops
+    B, H, N, D = 1, 2, 2000, 64                       # 15 full query blocks + one of 80 rows
+    q, k, v = _inputs(B, H, N, D, torch.bfloat16, 14)
+    q = q * 3
+    _, parts = O.spas_sage2_attn_meansim_topk(q, k, v, topk=0.6, pvthreshd=4.0, return_parts=True)
+    pv = O.hyperparameter_check(4.0, H)
+    nq = (N + 127) // 128
+    counts = torch.zeros(B, H, nq * 4, dtype=torch.int32)
+    ref, skipped = O.attention_blockwise(parts["q_int8"], parts["q_scale"], parts["k_int8"], parts["k_scale"], parts["v8"],
+                                         parts["v_scale"], parts["map"], D ** -0.5, pv, group_counts=counts)
+    lut, valid = O.block_map_to_lut(parts["map"])
+    dev = lambda t: t.cuda().contiguous()
+    o, cnt = ops.attn_fwd(dev(parts["q_int8"]), dev(parts["k_int8"]), dev(O.e4m3_bits(parts["v8"])), dev(lut.int()),
+                          dev(valid.int()), dev(pv), dev(parts["q_scale"]), dev(parts["k_scale"]), dev(parts["v_scale"]),
+                          D ** -0.5, False, torch.bfloat16, return_pv_count=True)
+    _status_ok()
+    _check(o, ref)
+    cnt = cnt.cpu().view(B, H, nq, 4)
+    counts = counts.view(B, H, nq, 4)
+    live = valid.int()
+    assert skipped > 0 and (cnt[:, :, :-1, 0] < live[:, :, :-1]).any()            # full blocks do drop products
+    assert torch.equal(cnt[:, :, -1], live[:, :, -1:].expand(B, H, 4))            # the partial block keeps all
+    assert torch.equal(counts[:, :, -1], live[:, :, -1:].expand(B, H, 4))
+    assert abs(int(cnt.sum()) - int(counts.sum())) <= max(4, 4 * skipped // 100)

@@ -12,8 +12,9 @@ from make_golden import golden_inputs
 
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_predictor_*.pt")))
 GOLDEN_GPU = sorted(p for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_gpu_*.pt"))
-                    if "_cdf_" not in os.path.basename(p))
+                    if "_cdf_" not in os.path.basename(p) and "_gran_" not in os.path.basename(p))
 GOLDEN_GPU_CDF = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_gpu_cdf_*.pt")))
+GOLDEN_GPU_GRAN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_gpu_gran_*.pt")))
 
 
 def test_fixtures_present():
@@ -190,3 +191,38 @@ def test_sampled_blockwise_attention_equals_the_block_loop(shape, causal, pv, ga
     pad = (-N) % 128
     o1b = torch.nn.functional.pad(o1, (0, 0, 0, pad)).view(B, H, -1, 128, D)[:, :, blocks].reshape(o2.shape)
     assert torch.allclose(o1b, o2, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("path", GOLDEN_GPU_GRAN, ids=[os.path.basename(p) for p in GOLDEN_GPU_GRAN])
+def test_granularities_match_compiled_reference_fixture(path):
+    """qk_quant_gran 2 and 3 of the reference's attention op, recorded on a B200 (make_ref_gpu_gran_golden.py): the
+    oracle's per-warp quantiser reproduces the reference's Triton per_warp_int8 bit for bit, and the oracle's
+    attention with per-warp / per-thread scales matches the op's outputs at the attention tolerance, with its
+    count of kept P.V products within 1 % of the op's PV_Count (the skip test is active: pvthreshd = 4)."""
+    from make_ref_gpu_golden import ref_gpu_inputs
+    g = torch.load(path)
+    B, H, N, D, topk, pv, seed = g["case"]
+    dtype = torch.bfloat16 if g["dtype"] == "bf16" else torch.float16
+    q, k, v = ref_gpu_inputs(B, H, N, D, dtype, seed)
+    q = q * 3
+    assert abs(float(q.double().sum() + k.double().sum() + v.double().sum()) - g["input_sum"]) < 1e-6
+    km = O.k_mean(k)
+    assert torch.equal(km.view(torch.int16), g["km"].view(torch.int16))
+    ksm = (k - km).to(dtype)
+    q8, qs, k8, ks = O.per_warp_int8(q, ksm)
+    for name, mine in (("q_int8", q8), ("q_scale", qs), ("k_int8", k8), ("k_scale", ks)):
+        assert torch.equal(mine, g[name]), f"{name}: {(mine != g[name]).sum().item()} of {mine.numel()} differ"
+    v8, vs = O.quant_v(v, g["recip_scale"])
+    pvt = O.hyperparameter_check(pv, H)
+    nq = (N + 127) // 128
+    live4 = g["map"].sum(-1).int().repeat_interleave(4, dim=-1)
+    for gran, ops_ in ((2, (q8, qs, k8, ks)), (3, O.per_thread_int8(q, ksm))):
+        counts = torch.zeros(B, H, nq * 4, dtype=torch.int32)
+        o, skipped = O.attention_blockwise(*ops_[:2], *ops_[2:], v8, vs, g["map"], D ** -0.5, pvt, out_dtype=dtype,
+                                           qk_quant_gran=gran, group_counts=counts)
+        m = O.precision_metric(o.float(), g[f"o_gran{gran}"].float())
+        assert m["Cossim"] >= 0.999 and m["L1"] <= 1e-2, (gran, m)
+        ref_counts = g[f"pv_count_gran{gran}"].view(B, H, nq * 4)
+        assert (ref_counts <= live4).all() and int((live4 - counts).sum()) == 4 * skipped
+        ref_skipped = int((live4 - ref_counts).sum())
+        assert abs(ref_skipped - 4 * skipped) <= max(4, ref_skipped // 100 * 4 // 4 + 4), (gran, ref_skipped, 4 * skipped)
