@@ -130,6 +130,17 @@ def compare(q, k, v, is_causal=False, topk=0.5, simthreshd1=-0.1, attention_sink
                            rp["k_scale"], r_vs, sm, False, q.dtype)
     rep["attn_same_operands"] = metric(o_arith, r_o)
     rep["attn_whole_path"] = metric(o, r_o)
+    if pv_arg is not None:
+        # skip decisions: the per-32-row-group counts of kept P.V products, same operands on both sides
+        _, r_cnt = RR.attention(rp["q_int8"], rp["k_int8"], r_v8, rp["lut"], rp["valid"], pv_t, rp["q_scale"], rp["k_scale"],
+                                r_vs, sm, q.dtype, return_pv_count=True)
+        _, cnt = ops.attn_fwd(rp["q_int8"], rp["k_int8"], r_v8_tok, rp["lut"], rp["valid"], pv_arg, rp["q_scale"],
+                              rp["k_scale"], r_vs, sm, False, q.dtype, return_pv_count=True)
+        rep["pv_count_neq"], rep["pv_count_entries"] = _neq(cnt.view(-1), r_cnt.view(-1)), cnt.numel()
+        rep["pv_kept_ref"], rep["pv_kept_ours"], rep["pv_live_x4"] = int(r_cnt.sum()), int(cnt.sum()), 4 * int(rp["valid"].sum())
+        where = torch.nonzero(cnt.view(B, H, -1) != r_cnt.view(B, H, -1))[:8]
+        rep["pv_count_first_differences"] = [(int(b_), int(h_), int(e_), int(cnt.view(B, H, -1)[b_, h_, e_]),
+                                              int(r_cnt.view(B, H, -1)[b_, h_, e_])) for b_, h_, e_ in where.tolist()]
     r_api = RR.api_topk(q, k, v, stable=True, topk=topk, is_causal=is_causal, simthreshd1=simthreshd1,
                         attention_sink=attention_sink, pvthreshd=pvthreshd) if cdfthreshd is None else None
     if r_api is not None:
@@ -231,6 +242,22 @@ def main():
         r["case"] = "small-cdf"
         report["cases"].append(r)
         print(json.dumps(r), flush=True)
+    if "skip" in want:
+        for shape, dtype, pv, gain in (((1, 2, 2000, 64), torch.bfloat16, 4.0, 3.0), ((1, 2, 3000, 128), torch.float16, 4.0, 3.0),
+                                       ((2, 2, 640, 64), torch.bfloat16, 2.0, 3.0)):
+            q, k, v = (t.to(dev) for t in small_inputs(*shape, dtype, 13))
+            r = compare(q * gain, k, v, topk=0.6, pvthreshd=pv)
+            r["case"] = "skip-small"
+            report["cases"].append(r)
+            print(json.dumps(r), flush=True)
+        q, k, v = synthetic.workload_qkv(2, dev, heads=4)
+        for pv in (5.0, 2.0):
+            r = compare(q, k, v, topk=0.5, pvthreshd=pv)
+            r["case"] = f"skip-cfg2-pv{pv:g}"
+            report["cases"].append(r)
+            print(json.dumps(r), flush=True)
+        del q, k, v
+        torch.cuda.empty_cache()
     if "gran" in want:
         for shape, dtype, pv in (((1, 2, 1000, 128), torch.bfloat16, 50.0), ((2, 2, 640, 64), torch.float16, 50.0),
                                  ((1, 2, 3000, 64), torch.bfloat16, 4.0)):

@@ -468,10 +468,12 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
                 qf = q8[b, h, r0:r1].float()
                 rows = r1 - r0
                 m = torch.full((rows,), MASK_VALUE, dtype=torch.float32)
-                # Rows of a partial last query block beyond N: the reference's Q tile holds zeros there, their scores are
-                # zero, and they take part in the skip test's maximum over the block (update_mo has no row mask,
-                # attn_utils.cuh:418-466): after the first block their running maximum is 0 and their difference 0, so a
-                # partial query block never skips with a positive threshold.  m_pad is that running maximum.
+                # Rows of a partial last query block beyond N take part in the skip test's maximum over the block
+                # (update_mo has no row mask, attn_utils.cuh:418-466).  The reference leaves them unfilled in shared
+                # memory (predicated load without fill, attn_utils.cuh:133), so what they hold is not defined; the
+                # CUDA kernel under test zero-fills them, and zeros are modelled here: zero scores, running maximum 0
+                # after the first block, difference 0, hence no skip in a partial query block with a positive
+                # threshold.  m_pad is that running maximum.
                 m_pad = MASK_VALUE
                 d = torch.ones(rows, dtype=torch.float32)
                 acc = torch.zeros(rows, D, dtype=torch.float32)
@@ -571,7 +573,7 @@ def attention_blockwise_sampled(q8, q_scale, k8, k_scale, v8, v_scale, block_map
         m_new = torch.maximum(m, rowmax)
         upd = act.clone()
         if pv_skip:
-            # padded rows of a partial last query block (zero Q rows, zero scores) take part, as in the reference
+            # padded rows of a partial last query block take part as zero rows (see attention_blockwise)
             delta = (rowmax - m).amax(dim=-1)
             skip = act & (n_it < cnt - 2) & (delta + thr <= 0)
             skipped += int(skip.sum())

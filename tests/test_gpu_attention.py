@@ -436,9 +436,10 @@ def test_per_warp_pv_threshold_mode_matches_oracle(gran):
 
 
 def test_partial_last_query_block_never_skips():
-    """The reference's skip test takes its maximum over all 128 rows of the Q tile, padded rows included (zero
-    scores, running maximum 0, difference 0: attn_utils.cuh:418-466 has no row mask), so a partial last query block
-    keeps every product while full blocks of the same head drop some. Kernel and oracle both reproduce that."""
+    """The reference's skip test takes its maximum over all 128 rows of the Q tile (attn_utils.cuh:418-466 has no row
+    mask); rows beyond N are left unfilled by its loader, so its decision in a partial last query block depends on
+    stale shared memory. This kernel zero-fills them: zero scores, running maximum 0, difference 0, so the partial
+    block keeps every product while full blocks of the same head drop some. Kernel and oracle agree on that."""
     from spargeattn_b200 import ops
     B, H, N, D = 1, 2, 2000, 64                       # 15 full query blocks + one of 80 rows
     q, k, v = _inputs(B, H, N, D, torch.bfloat16, 14)
