@@ -258,6 +258,15 @@ def main():
             print(json.dumps(r), flush=True)
         del q, k, v
         torch.cuda.empty_cache()
+        for idx, heads in ((1, 4), (3, 4)):
+            w = synthetic.WORKLOADS[idx]
+            q, k, v = synthetic.workload_qkv(idx, dev, heads=heads)
+            r = compare(q, k, v, is_causal=w["causal"], topk=w["topk"], pvthreshd=5.0)
+            r["case"] = f"skip-cfg{idx}-pv5"
+            report["cases"].append(r)
+            print(json.dumps(r), flush=True)
+            del q, k, v
+            torch.cuda.empty_cache()
     if "gran" in want:
         for shape, dtype, pv in (((1, 2, 1000, 128), torch.bfloat16, 50.0), ((2, 2, 640, 64), torch.float16, 50.0),
                                  ((1, 2, 3000, 64), torch.bfloat16, 4.0)):
