@@ -267,6 +267,26 @@ def main():
             print(json.dumps(r), flush=True)
             del q, k, v
             torch.cuda.empty_cache()
+    if "sage1" in want:
+        # Sage1 signatures (core.py:235-319): the reference runs its fp16-PV sm80 kernel with token-level causal masking;
+        # this library serves them from the FP8-PV kernel. API against API, stable sort on the reference side.
+        ref_core = RR.load()["core"]
+        jobs = [("small", small_inputs(1, 2, 3000, 128, torch.bfloat16, 14), False), ("small", small_inputs(2, 2, 1500, 64, torch.float16, 15), True)]
+        jobs += [(f"cfg{i}", tuple(t.cpu() for t in synthetic.workload_qkv(i, dev, heads=2)), synthetic.WORKLOADS[i]["causal"]) for i in (2, 3)]
+        for tag, (q, k, v), causal in jobs:
+            q, k, v = q.to(dev), k.to(dev), v.to(dev)
+            with RR.stable_sort(True):
+                r_o = ref_core.spas_sage_attn_meansim_topk_cuda(q, k, v, topk=0.5, is_causal=causal)
+                r_c = ref_core.spas_sage_attn_meansim_cuda(q, k, v, is_causal=causal, simthreshd1=0.3, cdfthreshd=0.95)
+            o = S.spas_sage_attn_meansim_topk_cuda(q, k, v, topk=0.5, is_causal=causal)
+            o_c = S.spas_sage_attn_meansim_cuda(q, k, v, is_causal=causal, simthreshd1=0.3, cdfthreshd=0.95)
+            r = {"case": f"sage1-{tag}", "shape": list(q.shape), "dtype": str(q.dtype).replace("torch.", ""), "causal": causal,
+                 "topk_api_vs_api": metric(o, r_o), "cdf_api_vs_api": metric(o_c, r_c)}
+            ops.check_device_status(dev)
+            report["cases"].append(r)
+            print(json.dumps(r), flush=True)
+            del q, k, v
+            torch.cuda.empty_cache()
     if "gran" in want:
         for shape, dtype, pv in (((1, 2, 1000, 128), torch.bfloat16, 50.0), ((2, 2, 640, 64), torch.float16, 50.0),
                                  ((1, 2, 3000, 64), torch.bfloat16, 4.0)):
