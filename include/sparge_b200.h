@@ -195,6 +195,19 @@ int sparge_attn_fwd_gran(const int8_t* q_int8, const int8_t* k_int8, const uint8
                          int32_t* pv_count, const int32_t* q_block_ranges, int q_blocks_max, int qk_quant_gran,
                          int pv_threshold_mode, sparge_stream_t stream);
 
+/* The same kernel with P and V in fp16 (tcgen05.mma kind::f16, fp32 accumulation) instead of e4m3: the arithmetic of
+ * the reference's fp16-PV op qk_int8_sv_f16_accum_f16_block_sparse_attn_inst_buf_with_pv_threshold
+ * (csrc/qattn/qk_int_sv_f16_cuda_sm80.cu, called by the Sage1-signature functions, spas_sage_attn/core.py:263,305),
+ * with its arguments: v_f16 is the caller's fp16 V [B,H,N,D], contiguous and 16-byte aligned (no quantiser, no
+ * v_scale, no padding: rows past N are read as zeros); per-block scales (qk_quant_gran 1); pvthreshd NULL = no skip
+ * test, else the per-block test; pv_count, q_block_ranges as in sparge_attn_fwd_rows. The fp16 tiles are twice as
+ * large, so one CTA runs per SM: about 1.6x the time of the FP8 kernel. */
+int sparge_attn_fwd_f16pv(const int8_t* q_int8, const int8_t* k_int8, const void* v_f16, void* o, const int32_t* lut,
+                          const int32_t* valid, const float* pvthreshd, const float* q_scale, const float* k_scale,
+                          int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal, float sm_scale,
+                          long long o_stride_b, long long o_stride_h, long long o_stride_n, int32_t* pv_count,
+                          const int32_t* q_block_ranges, int q_blocks_max, sparge_stream_t stream);
+
 /* Failure-detection self test: launches one warp that waits on a barrier nobody signals, for `slices` tries with
  * the suspend hint slice_ns (a try lasts about 4 us on a B200 whatever the hint; slices x max(slice_ns, 4000) may
  * not exceed 0.1 s), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into

@@ -441,7 +441,7 @@ def granular_scales(q_scale, k_scale, b, h, i, j, rows, cols, qk_quant_gran):
 
 def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_scale: float, pvthreshd,
                         token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True, q_blocks=None,
-                        qk_quant_gran: int = 1, pv_threshold_mode: int = 1, group_counts=None):
+                        qk_quant_gran: int = 1, pv_threshold_mode: int = 1, group_counts=None, pv_fp16: bool = False):
     """Oracle B: block-online emulation of csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:42-755 with the
     helpers of csrc/qattn/attn_utils.cuh (update_mo :418-466, exponentiate_r :391-415,
     RS_32_to_8 :581-596, normalize_d :757-811).  fp32 PV accumulation.
@@ -454,7 +454,9 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
     entries per block).  `pv_threshold_mode` 1: the skip test reduces over the 128-row block
     (PVThresholdMode::kPerBlock, sm89.cuh:322-345); 2: every 32-row group decides for itself (kPerWarp: the
     warp-level reduction of :317-320 only).  `group_counts`: optional int32 [B,H,nq*4] tensor that receives,
-    per 32-row group, the number of P.V products kept (the reference's PV_Count, sm89.cuh:355-358,650-656)."""
+    per 32-row group, the number of P.V products kept (the reference's PV_Count, sm89.cuh:355-358,650-656).
+    `pv_fp16`: the fp16-PV kernel of the Sage1 signatures (csrc/qattn/qk_int_sv_f16_cuda_sm80.cuh): v8 then holds
+    the fp16 values of V (as fp32), v_scale is ignored, P = 2^(t - m) without the FP8 offset is rounded to fp16."""
     B, H, N, D = q8.shape
     nq, nk = block_map.shape[-2:]
     c = sm_scale * LOG2E
@@ -512,20 +514,26 @@ def attention_blockwise(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_sca
                             if g0 >= rows or bool(keep[g0]):
                                 group_counts[b, h, i * 4 + g0 // 32] += 1
                     alpha = torch.exp2(m - m_new)
-                    p = torch.exp2(t - m_new.unsqueeze(-1) + S_FP8_OFFSET)
+                    if pv_fp16:
+                        p = torch.exp2(t - m_new.unsqueeze(-1))
+                        p_lo = p.to(torch.float16).float()
+                    else:
+                        p = torch.exp2(t - m_new.unsqueeze(-1) + S_FP8_OFFSET)
+                        p_lo = e4m3_round(p)
                     d_new = d * alpha + p.sum(dim=-1)
-                    acc_new = acc * alpha.unsqueeze(-1) + e4m3_round(p) @ v8[b, h, c0:c1]
+                    acc_new = acc * alpha.unsqueeze(-1) + p_lo @ v8[b, h, c0:c1]
                     # a group that drops the block keeps its state (its maximum cannot have risen: delta < 0)
                     m = torch.where(keep, m_new, m)
                     d = torch.where(keep, d_new, d)
                     acc = torch.where(keep.unsqueeze(-1), acc_new, acc)
                 if live:
-                    o[b, h, r0:r1] = acc / d.unsqueeze(-1) * v_scale[b, h].view(1, D)
+                    o[b, h, r0:r1] = acc / d.unsqueeze(-1) * (1.0 if pv_fp16 else v_scale[b, h].view(1, D))
     return o.to(out_dtype), skipped
 
 
 def attention_blockwise_sampled(q8, q_scale, k8, k_scale, v8, v_scale, block_map, sm_scale: float, pvthreshd,
-                                q_blocks, token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True):
+                                q_blocks, token_causal: bool = False, out_dtype=torch.bfloat16, pv_skip: bool = True,
+                                pv_fp16: bool = False):
     """`attention_blockwise` restricted to the query blocks in `q_blocks`, evaluated for all (batch, head,
     query block) samples at once: the loop runs over the position in each sample's live list, not over
     samples, so a few dozen blocks of a 100k-token sequence take seconds.  Same arithmetic, same visiting
@@ -579,15 +587,16 @@ def attention_blockwise_sampled(q8, q_scale, k8, k_scale, v8, v_scale, block_map
             skipped += int(skip.sum())
             upd = upd & ~skip
         alpha = torch.exp2(m - m_new)
-        p = torch.exp2(t - m_new.unsqueeze(-1) + S_FP8_OFFSET)
+        p = torch.exp2(t - m_new.unsqueeze(-1) + (0.0 if pv_fp16 else S_FP8_OFFSET))
         p = torch.where(dead, torch.zeros_like(p), p)
         d_new = d * alpha + p.sum(dim=-1)
-        acc_new = acc * alpha.unsqueeze(-1) + torch.matmul(e4m3_round(p), vblk[bi, hi, j])
+        p_lo = p.to(torch.float16).float() if pv_fp16 else e4m3_round(p)      # pv_fp16: see attention_blockwise
+        acc_new = acc * alpha.unsqueeze(-1) + torch.matmul(p_lo, vblk[bi, hi, j])
         u1, u2 = upd.view(S, 1), upd.view(S, 1, 1)
         m = torch.where(u1, m_new, m)
         d = torch.where(u1, d_new, d)
         acc = torch.where(u2, acc_new, acc)
-    o = acc / d.unsqueeze(-1) * v_scale[bi, hi].view(S, 1, D)
+    o = acc / d.unsqueeze(-1) * (1.0 if pv_fp16 else v_scale[bi, hi].view(S, 1, D))
     o = torch.where((row_ok & (cnt > 0).view(S, 1)).unsqueeze(-1), o, torch.zeros_like(o))
     return o.view(B, H, nb * BLKQ, D).to(out_dtype), skipped
 
@@ -635,9 +644,11 @@ def _prologue(q, k, v, tensor_layout):
 def spas_sage2_attn_meansim_topk(q, k, v, is_causal=False, scale=None, smooth_k=True, simthreshd1=-0.1,
                                  cdfthreshd=None, topk=0.5, pvthreshd=50, attention_sink=False,
                                  tensor_layout="HND", return_sparsity=False, token_causal=False,
-                                 blockwise=True, return_parts=False):
+                                 blockwise=True, return_parts=False, pv_fp16=False):
     """spas_sage_attn/core.py:105-169 (and :39-103 when `cdfthreshd` is given instead of `topk`).
-    `token_causal=False` reproduces the reference, which never forwards is_causal to its kernel."""
+    `token_causal=False` reproduces the reference, which never forwards is_causal to its kernel.
+    `token_causal=True, pv_fp16=True` is the Sage1-signature path (core.py:235-319): fp16 V, fp16 P.V, is_causal
+    forwarded to the kernel."""
     q, k, v, dt = _prologue(q, k, v, tensor_layout)
     H, D = q.shape[1], q.shape[-1]
     assert D in (64, 128)
@@ -645,11 +656,12 @@ def spas_sage2_attn_meansim_topk(q, k, v, is_causal=False, scale=None, smooth_k=
     pr = predictor(q, k, km, is_causal, simthreshd1, cdfthreshd, topk, attention_sink)
     sm_scale = scale if scale is not None else 1.0 / math.sqrt(D)
     pv = hyperparameter_check(pvthreshd, H)
-    v8, vs = quant_v(v)
+    v8, vs = (v.to(torch.float16).float(), None) if pv_fp16 else quant_v(v)
     if blockwise:
         o, _ = attention_blockwise(pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v8, vs, pr["map"],
-                                   sm_scale, pv, token_causal and is_causal, dt)
+                                   sm_scale, pv, token_causal and is_causal, dt, pv_fp16=pv_fp16)
     else:
+        assert not pv_fp16
         o = attention_dense_masked(pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v8, vs, pr["map"],
                                    sm_scale, token_causal and is_causal, dt)
     if tensor_layout == "NHD":

@@ -37,6 +37,7 @@ SIGNATURES = {
     "sparge_attn_fwd_rows": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _ll, _ll, _ll, _p, _p, _i, _p]),
     "sparge_attn_fwd_gran": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _ll, _ll, _ll, _p, _p, _i,
                                   _i, _i, _p]),
+    "sparge_attn_fwd_f16pv": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _ll, _ll, _ll, _p, _p, _i, _p]),
     "sparge_peer_alloc": (_i, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
     "sparge_peer_free": (_i, [_p]),
     "sparge_peer_open": (_i, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),

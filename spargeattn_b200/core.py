@@ -20,6 +20,12 @@ from . import ops
 # behaviour; True additionally masks key > query inside the kernel.
 SAGE2_TOKEN_LEVEL_CAUSAL = False
 
+# The Sage1-signature entry points of the reference (core.py:235-319) keep V in fp16 and run an fp16 P.V kernel.
+# True: they run the fp16-PV variant of the attention kernel here as well (one CTA per SM, about 1.6x the time);
+# False: they share the FP8-PV kernel of the Sage2 entry points (faster; output within cosine 0.9996 but only
+# 1.4-2.4 % relative L1 of the reference's, because V and P are rounded to e4m3).
+SAGE1_FP16_PV = True
+
 
 _knob_cache = {}
 
@@ -197,17 +203,21 @@ def _sparsity(valid_block_num, lut, causal_denominator):
 
 
 def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, topk, pvthreshd, attention_sink,
-                       tensor_layout, return_sparsity, kernel_causal, q_block_ranges=None, q_blocks_max=0):
+                       tensor_layout, return_sparsity, kernel_causal, q_block_ranges=None, q_blocks_max=0,
+                       pv_fp16=False):
     """The path of spas_sage_attn/core.py:105-169. `q_block_ranges` (int32 [B,H,2]: first 128-row query block, count)
     makes the attention kernel compute only those rows of each head (the multi-GPU row sharding); everything
-    before the attention kernel still covers the whole head, since every query block needs all keys."""
+    before the attention kernel still covers the whole head, since every query block needs all keys.
+    `pv_fp16`: V stays fp16 and the kernel multiplies fp16 P by fp16 V (core.py:246-263, the Sage1 signatures)."""
     q, k, v = _prologue(q, k, v, tensor_layout)
     headdim = q.size(-1)
     assert headdim in [64, 128], "headdim should be in [64, 128]. For other headdim, you can use padding and specify the softmax scale."
     rows = q.size(0) * q.size(1) * q.size(2)
     beside = CONCURRENT_PREP_MIN_ROWS <= rows <= CONCURRENT_PREP_MAX_ROWS
     s_q, s_v = _side_streams(q.device) if beside else (None, None)
-    if beside:
+    if pv_fp16:
+        v16 = v.to(torch.float16).contiguous()             # core.py:246-248: V is cast to fp16 whatever the input type
+    elif beside:
         (v_fp8, v_scale), v_done = _run_beside(s_v, lambda: ops.quant_v(v))
     km = ops.k_mean(k) if smooth_k else None
     pvthreshd = _pv_threshold_tensor(pvthreshd, q.size(-3), q.device)
@@ -218,13 +228,18 @@ def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthre
         attention_sink=attention_sink, BLKQ=128, BLKK=64, best_first=pvthreshd is None, q_stream=s_q)
     if scale is None:
         scale = 1.0 / (headdim ** 0.5)
-    if beside:
-        torch.cuda.current_stream(q.device).wait_event(v_done)
+    if pv_fp16:
+        o = ops.attn_fwd_f16pv(q_int8, k_int8, v16, lut, valid_block_num, pvthreshd, q_scale, k_scale, scale,
+                               kernel_causal, q.dtype, out=_empty_like_layout(q), q_block_ranges=q_block_ranges,
+                               q_blocks_max=q_blocks_max)
     else:
-        v_fp8, v_scale = ops.quant_v(v)
-    o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale,
-                     kernel_causal, q.dtype, out=_empty_like_layout(q), q_block_ranges=q_block_ranges,
-                     q_blocks_max=q_blocks_max)
+        if beside:
+            torch.cuda.current_stream(q.device).wait_event(v_done)
+        else:
+            v_fp8, v_scale = ops.quant_v(v)
+        o = ops.attn_fwd(q_int8, k_int8, v_fp8, lut, valid_block_num, pvthreshd, q_scale, k_scale, v_scale, scale,
+                         kernel_causal, q.dtype, out=_empty_like_layout(q), q_block_ranges=q_block_ranges,
+                         q_blocks_max=q_blocks_max)
     if tensor_layout == 'NHD':
         o = o.transpose(-2, -3)
     if return_sparsity:
@@ -282,11 +297,11 @@ def block_sparse_sage2_attn_cuda(q, k, v, mask_id=None, dropout_p=0.0, scale=Non
 def spas_sage_attn_meansim_cuda(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, smooth_k=True,
                                 simthreshd1=0.6, cdfthreshd=0.98, pvthreshd=50, attention_sink=False,
                                 tensor_layout="HND", output_dtype=torch.float16, return_sparsity=False):
-    """spas_sage_attn/core.py:235-276 -- Sage1 signature (cdf selection).  The reference runs an
-    fp16-PV mma.sync kernel here and forwards is_causal to it; this build serves it from the same
-    FP8-PV tcgen05 kernel with token-level causal masking."""
+    """spas_sage_attn/core.py:235-276 -- Sage1 signature (cdf selection).  The reference runs its fp16-PV
+    mma.sync kernel here on unquantised fp16 V and forwards is_causal to it; this build runs the fp16-PV
+    variant of the tcgen05 kernel (SAGE1_FP16_PV = False: the FP8-PV kernel) with token-level causal masking."""
     return _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, None, pvthreshd,
-                              attention_sink, tensor_layout, return_sparsity, bool(is_causal))
+                              attention_sink, tensor_layout, return_sparsity, bool(is_causal), pv_fp16=SAGE1_FP16_PV)
 
 
 @torch.compiler.disable
@@ -294,6 +309,6 @@ def spas_sage_attn_meansim_topk_cuda(q, k, v, attn_mask=None, dropout_p=0.0, is_
                                      smooth_k=True, simthreshd1=-0.1, cdfthreshd=None, topk=0.5, pvthreshd=50,
                                      attention_sink=False, tensor_layout="HND", output_dtype=torch.float16,
                                      return_sparsity=False):
-    """spas_sage_attn/core.py:278-319 -- Sage1 signature (top-k selection), token-level causal."""
+    """spas_sage_attn/core.py:278-319 -- Sage1 signature (top-k selection), token-level causal, fp16 P.V."""
     return _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthreshd, topk, pvthreshd,
-                              attention_sink, tensor_layout, return_sparsity, bool(is_causal))
+                              attention_sink, tensor_layout, return_sparsity, bool(is_causal), pv_fp16=SAGE1_FP16_PV)

@@ -38,16 +38,24 @@ constexpr float kMagic = 12582912.0f;
 constexpr float kFastScaleLimit = 0.0078125f;  // 2^-7: bounds the fast path's per-block weight error by 0.41 %
 
 
-template <int D>
+// PVF16: P and V in fp16 (tcgen05.mma kind::f16) instead of e4m3 -- the arithmetic of the reference's fp16-PV kernel
+// (csrc/qattn/qk_int_sv_f16_cuda_sm80.cuh), which its Sage1-signature entry points run. V then is the caller's fp16
+// tensor itself (no quantiser); a 64-key V tile is D/64 sub-tiles of [64 keys x 128 bytes] (64 channels each, 128B
+// swizzle), P is two sub-tiles of [128 rows x 128 bytes], one per block of a pair. The tiles are twice as large,
+// so one CTA fits per SM.
+template <int D, bool PVF16 = false>
 struct AttnShape {
   static constexpr int kStagesK = (D == 128) ? 2 : 4;   // ring slots, each holding a PAIR of 64-key tiles
   static constexpr int kStagesV = (D == 128) ? 2 : 4;
   static constexpr int kTileQ = 128 * D;
   static constexpr int kTileKV = 64 * D;
   static constexpr int kPairKV = 2 * kTileKV;
-  static constexpr int kTileP = 128 * 128;              // 128 rows x 128 keys of e4m3
-  static constexpr int kSmemBytes = 1024 + kTileQ + kTileP + (kStagesK + kStagesV) * kPairKV;
+  static constexpr int kTileV = PVF16 ? 2 * kTileKV : kTileKV;
+  static constexpr int kPairV = 2 * kTileV;
+  static constexpr int kTileP = PVF16 ? 2 * 128 * 128 : 128 * 128;   // 128 rows x 128 keys of e4m3 / fp16
+  static constexpr int kSmemBytes = 1024 + kTileQ + kTileP + kStagesK * kPairKV + kStagesV * kPairV;
   static constexpr int kTmemCols = 256;
+  static constexpr int kCtasPerSm = PVF16 ? 1 : 2;
   static constexpr uint32_t kSwizzle = (D == 128) ? kSwizzle128B : kSwizzle64B;
 };
 
@@ -192,6 +200,26 @@ __device__ __forceinline__ float chunk_exp(const uint32_t* sr, float c, float m,
   }
 }
 
+// PVF16: P = 2^(S*c - m) for 32 scores as fp16 (no offset: the values are at most 1), row sum in fp32 before the
+// rounding; written to the four 16-byte chunks chunk0 .. chunk0+3 of the row in a [128 x 128 B] swizzled sub-tile.
+__device__ __forceinline__ float chunk_exp_f16(const uint32_t* sr, float c, float m, int klim, uint32_t prow, int chunk0,
+                                               int rsw) {
+  uint32_t pr[4];
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < 32; k += 2) {
+    float p0 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 0]), c, -m));
+    float p1 = ex2_approx(fmaf(__int2float_rn((int)sr[k + 1]), c, -m));
+    p0 = (k + 0 < klim) ? p0 : 0.f;
+    p1 = (k + 1 < klim) ? p1 : 0.f;
+    sum += p0 + p1;
+    const __half2 h = __floats2half2_rn(p0, p1);
+    pr[(k >> 1) & 3] = *reinterpret_cast<const uint32_t*>(&h);
+    if ((k & 6) == 6) st_shared_v4(prow + (uint32_t)(((chunk0 + (k >> 3)) ^ rsw) << 4), pr);
+  }
+  return sum;
+}
+
 __device__ __forceinline__ void pair_sync(int id) {   // the two warps that share 32 query rows
   asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
 }
@@ -201,15 +229,15 @@ constexpr int kAttnThreads = 320;
 // GRAN = qk_quant_gran: 1 one Q scale per 128-row block, 2 one per 32-row group (the K scale is per 64-key block in
 // both), 3 per-thread Q/K scales. PV_MODE = PVThresholdMode: 0 no skip test, 1 the test decides per block, 2 per
 // 32-row group.
-template <int D, bool CAUSAL, int PV_MODE, typename OutT, int GRAN>
-__global__ void __launch_bounds__(kAttnThreads, 2)
+template <int D, bool CAUSAL, int PV_MODE, typename OutT, int GRAN, bool PVF16 = false>
+__global__ void __launch_bounds__(kAttnThreads, (AttnShape<D, PVF16>::kCtasPerSm))
 attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
             const __grid_constant__ CUtensorMap tmap_v, OutT* __restrict__ o, const int32_t* __restrict__ lut,
             const int32_t* __restrict__ valid, const float* __restrict__ pvthr, const float* __restrict__ q_scale,
             const float* __restrict__ k_scale, const float* __restrict__ v_scale, int32_t* dev_status, int N, int H,
             int nq, int nk, float sm_scale_log2, int one, long long osb, long long osh, long long osn,
             int32_t* __restrict__ pv_count, const int32_t* __restrict__ q_ranges) {
-  using Shape = AttnShape<D>;
+  using Shape = AttnShape<D, PVF16>;
   constexpr bool PV_SKIP = PV_MODE != 0, pv_per_warp = PV_MODE == 2, GRAN3 = GRAN == 3;
   constexpr int SK = Shape::kStagesK, SV = Shape::kStagesV;
   extern __shared__ uint8_t smem_raw[];
@@ -217,7 +245,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   uint8_t* sQ = smem;
   uint8_t* sP = smem + Shape::kTileQ;
   uint8_t* sK = sP + Shape::kTileP;                  // slot s: sK + s * kPairKV
-  uint8_t* sV = sK + SK * Shape::kPairKV;
+  uint8_t* sV = sK + SK * Shape::kPairKV;              // slot s: sV + s * kPairV
 
   __shared__ uint64_t bar_q, bar_k_full[SK], bar_k_empty[SK], bar_v_full[SV], bar_v_empty[SV], bar_s_full, bar_s_free,
       bar_p_ready, bar_o_done, bar_delta[2];
@@ -326,6 +354,16 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       // warps read them once S of that step is complete, which is ordered after the tiles' arrival. The ring
       // slot was last used eight steps ago; the wait above has just shown that step s - stages has retired.
       if (meta) s_meta[s & 7] = *meta;
+      if (PVF16 && !meta) {   // fp16 V: D/64 sub-tiles of 64 channels (128 bytes) per block
+        uint8_t* dst = ring + slot * Shape::kPairV;
+        mbar_arrive_expect_tx(&full[slot], (jb >= 0 ? 2 : 1) * Shape::kTileV);
+#pragma unroll
+        for (int nh = 0; nh < D / 64; nh++) {
+          tma_load_3d(dst + nh * 8192, map, &full[slot], nh * 128, ja * 64, bh);
+          if (jb >= 0) tma_load_3d(dst + Shape::kTileV + nh * 8192, map, &full[slot], nh * 128, jb * 64, bh);
+        }
+        return;
+      }
       uint8_t* dst = ring + slot * Shape::kPairKV;
       mbar_arrive_expect_tx(&full[slot], (jb >= 0 ? 2 : 1) * Shape::kTileKV);
       tma_load_3d(dst, map, &full[slot], 0, ja * 64, bh);
@@ -381,6 +419,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       constexpr uint32_t idesc_qk2 = make_idesc(2, 1, 1, 0, 0, 128, 128);  // s32 += s8 * s8, both K-major, two blocks
       constexpr uint32_t idesc_qk1 = make_idesc(2, 1, 1, 0, 0, 128, 64);   // odd last block
       constexpr uint32_t idesc_pv = make_idesc(1, 0, 0, 0, 1, 128, D);     // f32 += e4m3 * e4m3, B MN-major
+      constexpr uint32_t idesc_pv16 = make_idesc(1, 0, 0, 0, 1, 128, 64);  // f32 += f16 * f16, B MN-major, 64 channels
       constexpr uint32_t sbo = 8 * D;
       bool ok = mbar_wait(&bar_q, 0);
       // Every operand descriptor is built once: this thread shares its scheduler with four softmax warps,
@@ -398,6 +437,19 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         vd[ks] = make_smem_desc(smem_u32(sV) + ks * 32 * D, 64 * D, sbo, Shape::kSwizzle);
       }
       constexpr uint64_t kSlotStep = (uint64_t)(Shape::kPairKV >> 4);
+      // fp16 P.V of one block: per 64-channel sub-tile of V four instructions of 16 keys each
+      auto issue_pv16 = [&](int blk, uint32_t slot_ofs_bytes, uint32_t& started) {
+        const uint32_t pbase = smem_u32(sP) + blk * 16384, vbase = smem_u32(sV) + slot_ofs_bytes + blk * Shape::kTileV;
+#pragma unroll
+        for (int nh = 0; nh < D / 64; nh++) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ks++)
+            mma_f16_ss(tO + nh * 64, make_smem_desc(pbase + ks * 32, 16, 1024, kSwizzle128B),
+                       make_smem_desc(vbase + nh * 8192 + ks * 2048, 8192, 1024, kSwizzle128B), idesc_pv16,
+                       (ks > 0) ? 1u : started);
+        }
+        started = 1;
+      };
       auto issue_qk = [&](int s) {   // the caller has waited for the K tiles of step s
         const int slot = s % SK;
         tc_fence_after();
@@ -429,12 +481,15 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         ok = mbar_wait(&bar_p_ready, s & 1);
         if (!ok) break;
         tc_fence_after();
-        if (!(PV_SKIP && s_skip[0])) {
+        if (PVF16) {
+          if (!(PV_SKIP && s_skip[0])) issue_pv16(0, slot * Shape::kPairV, o_started);
+          if (nb == 2 && !(PV_SKIP && s_skip[1])) issue_pv16(1, slot * Shape::kPairV, o_started);
+        } else if (!(PV_SKIP && s_skip[0])) {
           mma_f8_ss(tO, pd[0], vd[0] + vofs, idesc_pv, o_started);
           mma_f8_ss(tO, pd[1], vd[1] + vofs, idesc_pv, 1u);
           o_started = 1;
         }
-        if (nb == 2 && !(PV_SKIP && s_skip[1])) {
+        if (!PVF16 && nb == 2 && !(PV_SKIP && s_skip[1])) {
           mma_f8_ss(tO, pd[2], vd[2] + vofs, idesc_pv, o_started);
           mma_f8_ss(tO, pd[3], vd[3] + vofs, idesc_pv, 1u);
           o_started = 1;
@@ -556,9 +611,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       // masked path with no visible key): the other groups' rows of the same block may be multiplied.
       if (PV_SKIP && own_skip) klim = 0;
       const bool exact = masked || own_skip || !(c < kFastScaleLimit);
+      // fp16 variant: this thread's block is sub-tile 0 or 1 of P, 8 keys per 16-byte chunk
+      const uint32_t prow16 = smem_u32(sP) + (second ? 16384u : 0u) + (uint32_t)row * 128u;
       float sum = 0.f;
       if (nch == 2) {   // the second 32 columns are still in registers
-        sum = GRAN3 ? chunk_exp_g(sr, c4, m, klim - kofs - 32, prow, (col0 >> 4) + 2, rsw)
+        sum = PVF16 ? chunk_exp_f16(sr, c, m, klim - kofs - 32, prow16, (kofs >> 3) + 4, rsw)
+              : GRAN3 ? chunk_exp_g(sr, c4, m, klim - kofs - 32, prow, (col0 >> 4) + 2, rsw)
               : exact ? chunk_exp<true>(sr, c, m, klim - kofs - 32, one, prow, (col0 >> 4) + 2, rsw)
                       : chunk_exp<false>(sr, c, m, 32, one, prow, (col0 >> 4) + 2, rsw);
         tmem_ld32(tS + col0, sr);            // the first 32 again: they did not stay in registers
@@ -568,7 +626,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_s_free);
-      sum += GRAN3 ? chunk_exp_g(sr, c4, m, klim - kofs, prow, col0 >> 4, rsw)
+      sum += PVF16 ? chunk_exp_f16(sr, c, m, klim - kofs, prow16, kofs >> 3, rsw)
+             : GRAN3 ? chunk_exp_g(sr, c4, m, klim - kofs, prow, col0 >> 4, rsw)
              : exact ? chunk_exp<true>(sr, c, m, klim - kofs, one, prow, col0 >> 4, rsw)
                      : chunk_exp<false>(sr, c, m, 32, one, prow, col0 >> 4, rsw);
       bool skip = false;
@@ -613,8 +672,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       // has its own, the sum of what its two warps (one per block of a pair) kept.
       if (PV_SKIP && pv_per_warp) npv = __float_as_int(s_rmax[1][0][row]) + __float_as_int(s_rmax[1][1][row]);
       if (pv_count && lane == 0 && half == 0) pv_count[row_id * 4 + wq] = npv;
-      const float inv = rcp_approx(s_rmax[0][0][row] + s_rmax[0][1][row]);
-      const float* vs = v_scale + (size_t)bh * D + half * (D / 2);
+      // A row that saw no key at all (token-level causal mask over every live block of its row of blocks) has an
+      // empty sum: it is written as zeros. (The reference gives such a row the plain average of V over the masked
+      // keys, because its mask value is a large finite number and exp2(mask - mask) = 1.)
+      const float dsum = s_rmax[0][0][row] + s_rmax[0][1][row];
+      const float inv = dsum > 0.f ? rcp_approx(dsum) : 0.f;
+      const float* vs = PVF16 ? nullptr : v_scale + (size_t)bh * D + half * (D / 2);   // fp16 V carries no scale
       OutT* orow = o + (size_t)(bh / H) * osb + (size_t)(bh % H) * osh + (size_t)qrow * osn + half * (D / 2);
 #pragma unroll
       for (int c0 = 0; c0 < D / 2; c0 += 32) {
@@ -624,8 +687,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-          const float a = __uint_as_float(ov[2 * i]) * inv * vs[c0 + 2 * i];
-          const float bb = __uint_as_float(ov[2 * i + 1]) * inv * vs[c0 + 2 * i + 1];
+          const float a = __uint_as_float(ov[2 * i]) * inv * (PVF16 ? 1.f : vs[c0 + 2 * i]);
+          const float bb = __uint_as_float(ov[2 * i + 1]) * inv * (PVF16 ? 1.f : vs[c0 + 2 * i + 1]);
           w[i] = pack2<OutT>(a, bb);
         }
         if (qrow < N) {
@@ -660,26 +723,29 @@ static EncodeTiledFn encode_fn() {
 }
 
 // Byte tensor [planes, rows, inner] with a [1, box_rows, inner] box, swizzle span = inner bytes.
-static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t rows, uint64_t planes, uint32_t box_rows) {
+// box_inner: bytes of a row that one copy takes (default: the whole row); x coordinates are multiples of it.
+static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t rows, uint64_t planes, uint32_t box_rows,
+                     uint32_t box_inner = 0) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return false;
+  if (box_inner == 0) box_inner = (uint32_t)inner;
   cuuint64_t dims[3] = {inner, rows, planes};
   cuuint64_t strides[2] = {inner, inner * rows};
-  cuuint32_t box[3] = {(cuuint32_t)inner, box_rows, 1};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
   cuuint32_t es[3] = {1, 1, 1};
-  const CUtensorMapSwizzle sw = inner == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUtensorMapSwizzle sw = box_inner == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, es,
              CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, bool CAUSAL, int PV_MODE, typename OutT, int GRAN>
+template <int D, bool CAUSAL, int PV_MODE, typename OutT, int GRAN, bool PVF16 = false>
 static int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, const int32_t* lut,
                        const int32_t* valid, const float* pvthr, const float* qs, const float* ks, const float* vs,
                        int32_t* status, int BH, int H, int N, float sm_scale_log2, long long osb, long long osh,
                        long long osn, int32_t* pv_count, const int32_t* q_ranges, int q_blocks_max, cudaStream_t st) {
-  auto kern = attn_kernel<D, CAUSAL, PV_MODE, OutT, GRAN>;
-  constexpr int smem = AttnShape<D>::kSmemBytes;
+  auto kern = attn_kernel<D, CAUSAL, PV_MODE, OutT, GRAN, PVF16>;
+  constexpr int smem = AttnShape<D, PVF16>::kSmemBytes;
   // function attributes are per device: set on every call (cheap) rather than caching
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return SPARGE_ERR_CUDA;
   cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -758,6 +824,41 @@ extern "C" int sparge_attn_fwd_gran(const int8_t* q_int8, const int8_t* k_int8, 
 #undef SPARGE_ATTN_T
 #undef SPARGE_ATTN
 #undef SPARGE_ATTN_G
+}
+
+extern "C" int sparge_attn_fwd_f16pv(const int8_t* q_int8, const int8_t* k_int8, const void* v_f16, void* o,
+                                     const int32_t* lut, const int32_t* valid, const float* pvthreshd,
+                                     const float* q_scale, const float* k_scale, int32_t* dev_status, int B, int H, int N,
+                                     int D, int out_dtype, int is_causal, float sm_scale, long long o_stride_b,
+                                     long long o_stride_h, long long o_stride_n, int32_t* pv_count,
+                                     const int32_t* q_block_ranges, int q_blocks_max, sparge_stream_t stream) {
+  using namespace sparge;
+  if (q_block_ranges && q_blocks_max <= 0) return SPARGE_ERR_INVALID_ARG;
+  if (!q_int8 || !k_int8 || !v_f16 || !o || !lut || !valid || !q_scale || !k_scale) return SPARGE_ERR_NULL;
+  if (B <= 0 || H <= 0 || N <= 0 || (D != 64 && D != 128) || (out_dtype != SPARGE_F16 && out_dtype != SPARGE_BF16))
+    return SPARGE_ERR_INVALID_ARG;
+  if (!(sm_scale > 0.f) || (reinterpret_cast<uintptr_t>(v_f16) & 15)) return SPARGE_ERR_INVALID_ARG;
+  if ((long long)B * H > 65535) return SPARGE_ERR_TOO_LARGE;
+  if (!strides_ok(o, o_stride_b, o_stride_h, o_stride_n)) return SPARGE_ERR_INVALID_ARG;
+  const int BH = B * H;
+  CUtensorMap tq, tk, tv;
+  // V as bytes: rows of 2 D bytes, copied 128 bytes (64 channels) at a time; rows past N read as zeros
+  if (!make_map(&tq, q_int8, D, N, BH, 128) || !make_map(&tk, k_int8, D, N, BH, 64) ||
+      !make_map(&tv, v_f16, 2 * (uint64_t)D, N, BH, 64, 128))
+    return SPARGE_ERR_CUDA;
+  cudaStream_t st = (cudaStream_t)stream;
+  const float sl2 = sm_scale * kLog2e;
+  const bool causal = is_causal != 0, bf = out_dtype == SPARGE_BF16, skip = pvthreshd != nullptr;
+#define SPARGE_F16PV(DD, C, S, T) \
+  launch_attn<DD, C, S, T, 1, true>(tq, tk, tv, o, lut, valid, pvthreshd, q_scale, k_scale, nullptr, dev_status, BH, H, N, sl2, o_stride_b, o_stride_h, o_stride_n, pv_count, q_block_ranges, q_blocks_max, st)
+#define SPARGE_F16PV_T(DD, C, S) (bf ? SPARGE_F16PV(DD, C, S, __nv_bfloat16) : SPARGE_F16PV(DD, C, S, __half))
+#define SPARGE_F16PV_S(DD, C) (skip ? SPARGE_F16PV_T(DD, C, 1) : SPARGE_F16PV_T(DD, C, 0))
+#define SPARGE_F16PV_C(DD) (causal ? SPARGE_F16PV_S(DD, true) : SPARGE_F16PV_S(DD, false))
+  return D == 64 ? SPARGE_F16PV_C(64) : SPARGE_F16PV_C(128);
+#undef SPARGE_F16PV_C
+#undef SPARGE_F16PV_S
+#undef SPARGE_F16PV_T
+#undef SPARGE_F16PV
 }
 
 extern "C" int sparge_attn_fwd_rows(const int8_t* q_int8, const int8_t* k_int8, const uint8_t* v8, void* o,

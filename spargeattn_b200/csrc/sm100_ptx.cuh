@@ -239,6 +239,17 @@ __device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint
       : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem], fp16 inputs (instruction-descriptor formats 0 / 0), f32 accumulate, K = 16.
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- numeric helpers
 // Two floats -> two e4m3 bytes (round to nearest even, saturate to +-448). lo goes to bits [7:0].
 __device__ __forceinline__ uint16_t cvt_e4m3x2(float lo, float hi) {

@@ -210,6 +210,30 @@ def attn_fwd(q8, k8, v8, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale,
     return (out, pv_count) if return_pv_count else out
 
 
+def attn_fwd_f16pv(q8, k8, v16, lut, valid, pvthreshd: Optional[torch.Tensor], q_scale, k_scale, sm_scale: float,
+                   is_causal: bool, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
+                   return_pv_count: bool = False, q_block_ranges: Optional[torch.Tensor] = None, q_blocks_max: int = 0):
+    """Block-sparse attention with fp16 P and V (the reference's fp16-PV op, core.py:263): v16 is fp16 [B,H,N,D],
+    contiguous; everything else as attn_fwd with per-block scales."""
+    _need_cuda(q8, k8, v16, lut, valid, pvthreshd, q_scale, k_scale, q_block_ranges)
+    assert v16.dtype == torch.float16 and v16.is_contiguous(), "v must be a contiguous fp16 [B,H,N,D] tensor"
+    B, H, N, D = q8.shape
+    assert tuple(v16.shape) == (B, H, N, D)
+    if out is None:
+        out = torch.empty(B, H, N, D, dtype=out_dtype, device=q8.device)
+    _need_strided(out)
+    status = device_status_word(q8.device)
+    pv_count = torch.empty(B, H, (N + 127) // 128 * 4, dtype=torch.int32, device=q8.device) if return_pv_count else None
+    if q_block_ranges is not None:
+        assert q_block_ranges.dtype == torch.int32 and q_block_ranges.numel() == 2 * B * H and q_blocks_max > 0
+    _cabi.check(_cabi.lib.sparge_attn_fwd_f16pv(_ptr(q8), _ptr(k8), _ptr(v16), _ptr(out), _ptr(lut), _ptr(valid),
+                                                _ptr(pvthreshd), _ptr(q_scale), _ptr(k_scale), _ptr(status), B, H, N, D,
+                                                _dt(out), int(bool(is_causal)), float(sm_scale), out.stride(0),
+                                                out.stride(1), out.stride(2), _ptr(pv_count), _ptr(q_block_ranges),
+                                                int(q_blocks_max), _stream(q8)), "sparge_attn_fwd_f16pv")
+    return (out, pv_count) if return_pv_count else out
+
+
 def tensor_peak(kind: str = "i8", n: int = 128, ctas_per_sm: int = 2, target_ms: float = 50.0, device=None) -> dict:
     """Sustained tcgen05.mma rate of the current device for 8-bit operands (M = 128, N = n, K = 32 per
     instruction, operands resident in shared memory): {"tops", "ms", "kind", "n", "ctas_per_sm"}.

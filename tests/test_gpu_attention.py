@@ -56,7 +56,8 @@ def test_causal_variants(D, kernel_causal):
     import spargeattn_b200 as S
     B, H, N = 1, 2, 1100
     q, k, v = _inputs(B, H, N, D, torch.bfloat16, 11)
-    o_ref = O.spas_sage2_attn_meansim_topk(q, k, v, is_causal=True, topk=0.5, token_causal=kernel_causal)
+    o_ref = O.spas_sage2_attn_meansim_topk(q, k, v, is_causal=True, topk=0.5, token_causal=kernel_causal,
+                                           pv_fp16=kernel_causal)           # the Sage1 signatures multiply in fp16
     fn = S.spas_sage_attn_meansim_topk_cuda if kernel_causal else S.spas_sage2_attn_meansim_topk_cuda
     o = fn(q.cuda(), k.cuda(), v.cuda(), is_causal=True, topk=0.5)
     _status_ok()
@@ -464,3 +465,84 @@ def test_partial_last_query_block_never_skips():
     assert torch.equal(cnt[:, :, -1], live[:, :, -1:].expand(B, H, 4))            # the partial block keeps all
     assert torch.equal(counts[:, :, -1], live[:, :, -1:].expand(B, H, 4))
     assert abs(int(cnt.sum()) - int(counts.sum())) <= max(4, 4 * skipped // 100)
+
+
+@pytest.mark.parametrize("N,D,causal,topk", [(1500, 128, False, 0.5), (1000, 64, False, 0.6), (900, 128, True, 0.5),
+                                             (2100, 64, True, 0.4), (130, 128, False, 1.0), (4096, 128, False, 0.1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fp16_pv_kernel_matches_oracle(N, D, causal, topk, dtype):
+    """The fp16-PV variant (tcgen05 kind::f16; the arithmetic of the reference's Sage1 kernel): unquantised fp16 V,
+    P rounded to fp16 without the FP8 offset. Against the oracle in that mode at the attention tolerance; it must
+    also be markedly closer to an fp32 attention on the same INT8 Q/K than the FP8 kernel is."""
+    from spargeattn_b200 import ops
+    B, H = 1, 2
+    q, k, v = _inputs(B, H, N, D, dtype, 61)
+    km = O.k_mean(k)
+    pr = O.predictor(q, k, km, causal, torch.full((H,), -0.1), None, torch.full((H,), topk), False)
+    lut, valid = O.block_map_to_lut(pr["map"])
+    v16 = v.to(torch.float16)
+    dev = lambda t: t.cuda().contiguous()
+    args = (dev(pr["q_int8"]), dev(pr["k_int8"]))
+    o = ops.attn_fwd_f16pv(*args, dev(v16), dev(lut.int()), dev(valid.int()), None, dev(pr["q_scale"]), dev(pr["k_scale"]),
+                           D ** -0.5, causal, dtype)
+    _status_ok()
+    ref, _ = O.attention_blockwise(pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v16.float(), None, pr["map"],
+                                   D ** -0.5, None, token_causal=causal, out_dtype=dtype, pv_skip=False, pv_fp16=True)
+    m = _check(o, ref)
+    assert m["L1"] <= 3e-3, m                               # fp16 products: an order of magnitude inside the FP8 bar
+    # against exact P and V (fp32 softmax on the de-quantised Q/K under the same mask): fp16 PV is closer than FP8 PV
+    v8, vs = O.quant_v(v)
+    exact = O.attention_dense_masked(pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v16.float(),
+                                     torch.ones(B, H, D), pr["map"], D ** -0.5, token_causal=causal, out_dtype=torch.float32)
+    o8 = ops.attn_fwd(*args, dev(O.e4m3_bits(v8)), dev(lut.int()), dev(valid.int()), None, dev(pr["q_scale"]),
+                      dev(pr["k_scale"]), dev(vs), D ** -0.5, causal, dtype)
+    e16 = O.precision_metric(o.float().cpu(), exact)["L1"]
+    e8 = O.precision_metric(o8.float().cpu(), exact)["L1"]
+    assert e16 < 0.5 * e8, (e16, e8)
+
+
+def test_fp16_pv_skip_counts_and_sage1_api():
+    """fp16-PV kernel with the skip test: counts against the oracle in that mode; and the Sage1-signature entry points
+    (what the reference serves with its fp16-PV kernel) run it, token-level causal included."""
+    import spargeattn_b200 as S
+    from spargeattn_b200 import core, ops
+    B, H, N, D = 1, 2, 2048, 64
+    q, k, v = _inputs(B, H, N, D, torch.bfloat16, 14)
+    q = q * 3
+    km = O.k_mean(k)
+    pr = O.predictor(q, k, km, False, torch.full((H,), -0.1), None, torch.full((H,), 0.6), False)
+    lut, valid = O.block_map_to_lut(pr["map"])
+    pv = O.hyperparameter_check(4.0, H)
+    v16 = v.to(torch.float16)
+    dev = lambda t: t.cuda().contiguous()
+    o, cnt = ops.attn_fwd_f16pv(dev(pr["q_int8"]), dev(pr["k_int8"]), dev(v16), dev(lut.int()), dev(valid.int()), dev(pv),
+                                dev(pr["q_scale"]), dev(pr["k_scale"]), D ** -0.5, False, torch.bfloat16, return_pv_count=True)
+    _status_ok()
+    counts = torch.zeros(B, H, valid.shape[-1] * 4, dtype=torch.int32)
+    ref, skipped = O.attention_blockwise(pr["q_int8"], pr["q_scale"], pr["k_int8"], pr["k_scale"], v16.float(), None,
+                                         pr["map"], D ** -0.5, pv, pv_fp16=True, group_counts=counts)
+    _check(o, ref)
+    assert skipped > 0 and abs(int(cnt.cpu().sum()) - int(counts.sum())) <= max(4, 4 * skipped // 100)
+    # public Sage1 signatures: fp16 PV by default, the FP8 kernel when switched off; both near the same answer
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    for causal in (False, True):
+        a = S.spas_sage_attn_meansim_topk_cuda(qc, kc, vc, topk=0.6, is_causal=causal)
+        try:
+            core.SAGE1_FP16_PV = False
+            b = S.spas_sage_attn_meansim_topk_cuda(qc, kc, vc, topk=0.6, is_causal=causal)
+        finally:
+            core.SAGE1_FP16_PV = True
+        _status_ok()
+        m = O.precision_metric(a.float().cpu(), b.float().cpu())
+        assert m["Cossim"] > 0.999 and 1e-4 < m["L1"] < 5e-2, m
+        # cdf selection keeps a single block for many rows of blocks here; under the token-level causal mask some
+        # rows then see no key at all: they are zeros, never NaN
+        c = S.spas_sage_attn_meansim_cuda(qc, kc, vc, is_causal=causal, simthreshd1=0.3, cdfthreshd=0.95)
+        assert torch.isfinite(c.float()).all()
+        try:
+            core.SAGE1_FP16_PV = False
+            c8 = S.spas_sage_attn_meansim_cuda(qc, kc, vc, is_causal=causal, simthreshd1=0.3, cdfthreshd=0.95)
+        finally:
+            core.SAGE1_FP16_PV = True
+        assert torch.isfinite(c8.float()).all()
+        assert torch.equal((c.float().abs().sum(-1) == 0), (c8.float().abs().sum(-1) == 0))     # the same empty rows

@@ -148,11 +148,13 @@ def _select_bit_exact(dev, fr, topk, causal):
     return fmap
 
 
-def _attention_on_sample(o_gpu, fr, fmap, D, pvthreshd, token_causal, blocks):
+def _attention_on_sample(o_gpu, fr, fmap, D, pvthreshd, token_causal, blocks, v16=None):
+    """v16: the fp16 values of V for the fp16-PV kernel of the Sage1 signatures (None: FP8 V of the Sage2 path)."""
     H, N = fr["q8"].shape[1], fr["q8"].shape[2]
     pv = O.hyperparameter_check(float(pvthreshd), H)
-    o_ref, _ = O.attention_blockwise_sampled(fr["q8"], fr["qs"], fr["k8"], fr["ks"], fr["v8"], fr["vs"], fmap, D ** -0.5,
-                                             pv, blocks, token_causal, torch.bfloat16)
+    o_ref, _ = O.attention_blockwise_sampled(fr["q8"], fr["qs"], fr["k8"], fr["ks"], fr["v8"] if v16 is None else v16,
+                                             fr["vs"], fmap, D ** -0.5, pv, blocks, token_causal, torch.bfloat16,
+                                             pv_fp16=v16 is not None)
     B = o_ref.shape[0]
     pad = (-N) % 128
     og = torch.nn.functional.pad(o_gpu.float().cpu(), (0, 0, 0, pad)).view(B, H, -1, 128, D)[:, :, blocks].reshape(o_ref.shape)
@@ -198,7 +200,7 @@ def test_workload_sizes_bit_exact_preprocessing_and_sampled_attention(idx, n_cut
         if causal:       # the Sage1-signature entry point masks key > query inside the kernel as well
             o = S.spas_sage_attn_meansim_topk_cuda(qc, kc, vc, topk=topk, is_causal=True)
             ops.check_device_status()
-            _attention_on_sample(o, fr, fmap, D, 50.0, True, blocks[:12])
+            _attention_on_sample(o, fr, fmap, D, 50.0, True, blocks[:12], v16=v.to(torch.float16).float())
 
 
 @pytest.mark.parametrize("n_cut", [None, 17550])
