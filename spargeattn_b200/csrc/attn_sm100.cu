@@ -41,12 +41,12 @@ constexpr float kFastScaleLimit = 0.0078125f;  // 2^-7: bounds the fast path's p
 // PVF16: P and V in fp16 (tcgen05.mma kind::f16) instead of e4m3 -- the arithmetic of the reference's fp16-PV kernel
 // (csrc/qattn/qk_int_sv_f16_cuda_sm80.cuh), which its Sage1-signature entry points run. V then is the caller's fp16
 // tensor itself (no quantiser); a 64-key V tile is D/64 sub-tiles of [64 keys x 128 bytes] (64 channels each, 128B
-// swizzle), P is two sub-tiles of [128 rows x 128 bytes], one per block of a pair. The tiles are twice as large,
-// so one CTA fits per SM.
+// swizzle), P is two sub-tiles of [128 rows x 128 bytes], one per block of a pair. The tiles are twice as large:
+// at D = 128 one CTA fits per SM, at D = 64 two (with two ring slots instead of four).
 template <int D, bool PVF16 = false>
 struct AttnShape {
-  static constexpr int kStagesK = (D == 128) ? 2 : 4;   // ring slots, each holding a PAIR of 64-key tiles
-  static constexpr int kStagesV = (D == 128) ? 2 : 4;
+  static constexpr int kStagesK = (D == 128 || PVF16) ? 2 : 4;   // ring slots, each holding a PAIR of 64-key tiles
+  static constexpr int kStagesV = (D == 128 || PVF16) ? 2 : 4;
   static constexpr int kTileQ = 128 * D;
   static constexpr int kTileKV = 64 * D;
   static constexpr int kPairKV = 2 * kTileKV;
@@ -55,7 +55,7 @@ struct AttnShape {
   static constexpr int kTileP = PVF16 ? 2 * 128 * 128 : 128 * 128;   // 128 rows x 128 keys of e4m3 / fp16
   static constexpr int kSmemBytes = 1024 + kTileQ + kTileP + kStagesK * kPairKV + kStagesV * kPairV;
   static constexpr int kTmemCols = 256;
-  static constexpr int kCtasPerSm = PVF16 ? 1 : 2;
+  static constexpr int kCtasPerSm = (PVF16 && D == 128) ? 1 : 2;   // fp16 tiles at D = 128: 145 KB of shared memory
   static constexpr uint32_t kSwizzle = (D == 128) ? kSwizzle128B : kSwizzle64B;
 };
 
@@ -202,9 +202,28 @@ __device__ __forceinline__ float chunk_exp(const uint32_t* sr, float c, float m,
 
 // PVF16: P = 2^(S*c - m) for 32 scores as fp16 (no offset: the values are at most 1), row sum in fp32 before the
 // rounding; written to the four 16-byte chunks chunk0 .. chunk0+3 of the row in a [128 x 128 B] swizzled sub-tile.
-__device__ __forceinline__ float chunk_exp_f16(const uint32_t* sr, float c, float m, int klim, uint32_t prow, int chunk0,
-                                               int rsw) {
+template <bool EXACT>
+__device__ __forceinline__ float chunk_exp_f16(const uint32_t* sr, float c, float m, int klim, int one, uint32_t prow,
+                                               int chunk0, int rsw) {
   uint32_t pr[4];
+  if (!EXACT) {   // same int->float bias trick and packed arithmetic as the e4m3 path (see chunk_exp)
+    const float off = fmaf(-kMagic, c, -m);
+    const float2 c2 = make_float2(c, c), o2 = make_float2(off, off);
+    float2 s0 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 32; k += 2) {
+      float2 a = make_float2(__int_as_float((int)sr[k + 0] * one + (int)kMagicBits),
+                             __int_as_float((int)sr[k + 1] * one + (int)kMagicBits));
+      a = __ffma2_rn(a, c2, o2);
+      a.x = ex2_approx(a.x);
+      a.y = ex2_approx(a.y);
+      s0 = __fadd2_rn(s0, a);
+      const __half2 h = __floats2half2_rn(a.x, a.y);
+      pr[(k >> 1) & 3] = *reinterpret_cast<const uint32_t*>(&h);
+      if ((k & 6) == 6) st_shared_v4(prow + (uint32_t)(((chunk0 + (k >> 3)) ^ rsw) << 4), pr);
+    }
+    return s0.x + s0.y;
+  }
   float sum = 0.f;
 #pragma unroll
   for (int k = 0; k < 32; k += 2) {
@@ -615,7 +634,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       const uint32_t prow16 = smem_u32(sP) + (second ? 16384u : 0u) + (uint32_t)row * 128u;
       float sum = 0.f;
       if (nch == 2) {   // the second 32 columns are still in registers
-        sum = PVF16 ? chunk_exp_f16(sr, c, m, klim - kofs - 32, prow16, (kofs >> 3) + 4, rsw)
+        sum = PVF16 ? (exact ? chunk_exp_f16<true>(sr, c, m, klim - kofs - 32, one, prow16, (kofs >> 3) + 4, rsw)
+                             : chunk_exp_f16<false>(sr, c, m, 32, one, prow16, (kofs >> 3) + 4, rsw))
               : GRAN3 ? chunk_exp_g(sr, c4, m, klim - kofs - 32, prow, (col0 >> 4) + 2, rsw)
               : exact ? chunk_exp<true>(sr, c, m, klim - kofs - 32, one, prow, (col0 >> 4) + 2, rsw)
                       : chunk_exp<false>(sr, c, m, 32, one, prow, (col0 >> 4) + 2, rsw);
@@ -626,7 +646,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_s_free);
-      sum += PVF16 ? chunk_exp_f16(sr, c, m, klim - kofs, prow16, kofs >> 3, rsw)
+      sum += PVF16 ? (exact ? chunk_exp_f16<true>(sr, c, m, klim - kofs, one, prow16, kofs >> 3, rsw)
+                            : chunk_exp_f16<false>(sr, c, m, 32, one, prow16, kofs >> 3, rsw))
              : GRAN3 ? chunk_exp_g(sr, c4, m, klim - kofs, prow, col0 >> 4, rsw)
              : exact ? chunk_exp<true>(sr, c, m, klim - kofs, one, prow, col0 >> 4, rsw)
                      : chunk_exp<false>(sr, c, m, 32, one, prow, col0 >> 4, rsw);
