@@ -51,6 +51,9 @@ def parse():
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads, comparators and the reference-on-GPU leg")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=2)
     ap.add_argument("--quick", action="store_true", help="device-resident arm only (for profiler runs)")
+    ap.add_argument("--api", default="sage2", choices=["sage2", "sage1"],
+                    help="sage2: spas_sage2_attn_meansim_topk_cuda (INT8 QK, FP8 PV; the benchmark); sage1: the Sage1-signature "
+                         "entry point spas_sage_attn_meansim_topk_cuda (fp16 PV, token-level causal), device-resident arm only")
     ap.add_argument("--share", default=None, metavar="R/W",
                     help="single process: run the share that rank R of a W-GPU job would own (the row sharding has no "
                          "collective, so one GPU can time any rank's share); the printed value assumes every rank takes as long")
@@ -368,7 +371,11 @@ def main():
     whole = all(a == 0 and n == nq for (_, _, a, n) in units)
     ranges = torch.tensor([[a, n] for (_, _, a, n) in units], dtype=torch.int32).view(1, len(units), 2)
     ranges_dev, ranges_max = ranges.to(dev), int(ranges[..., 1].max())
-    if whole:     # every owned head is complete: the public entry point itself
+    if args.api == "sage1":
+        assert whole and args.quick, "--api sage1 times whole heads, device-resident arm only (--quick)"
+        api = lambda a, b, c: S.spas_sage_attn_meansim_topk_cuda(a, b, c, topk=topk, is_causal=causal,
+                                                                pvthreshd=args.pvthreshd)
+    elif whole:     # every owned head is complete: the public entry point itself
         api = lambda a, b, c: S.spas_sage2_attn_meansim_topk_cuda(a, b, c, topk=topk, is_causal=causal,
                                                                  pvthreshd=args.pvthreshd)
     else:
