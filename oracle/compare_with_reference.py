@@ -267,6 +267,53 @@ def main():
             print(json.dumps(r), flush=True)
             del q, k, v
             torch.cuda.empty_cache()
+    if "knobs" in want:
+        # the public knobs, API against API on one input: attention sink, self-similarity threshold, per-head tensors,
+        # NHD layout, return_sparsity, the cdf entry point, the block-sparse entry point
+        ref_core = RR.load()["core"]
+        q, k, v = (t.to(dev) for t in small_inputs(2, 4, 2500, 128, torch.bfloat16, 16))
+        H = q.shape[1]
+        per_head = torch.tensor([0.2, 0.4, 0.6, 0.8], device=dev)
+        jobs = {
+            "sink": dict(topk=0.3, attention_sink=True),
+            "simthreshd1_0.5": dict(topk=0.3, simthreshd1=0.5),
+            "per_head_topk": dict(topk=per_head),
+            "per_head_simthreshd1": dict(topk=0.4, simthreshd1=per_head),
+            "causal_sink": dict(topk=0.5, is_causal=True, attention_sink=True),
+            "pvthreshd_3": dict(topk=0.6, pvthreshd=3.0),
+            "scale_0.05": dict(topk=0.5, scale=0.05),
+        }
+        for name, kw in jobs.items():
+            with RR.stable_sort(True):
+                r_o, r_s = ref_core.spas_sage2_attn_meansim_topk_cuda(q, k, v, return_sparsity=True, **kw)
+            o, s_ = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, return_sparsity=True, **kw)
+            r = {"case": f"knobs-{name}", "api_vs_api": metric(o, r_o), "sparsity_ref": r_s, "sparsity_ours": s_}
+            report["cases"].append(r)
+            print(json.dumps(r), flush=True)
+        # NHD layout
+        qn, kn, vn = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+        with RR.stable_sort(True):
+            r_o = ref_core.spas_sage2_attn_meansim_topk_cuda(qn, kn, vn, topk=0.5, tensor_layout="NHD")
+        o = S.spas_sage2_attn_meansim_topk_cuda(qn, kn, vn, topk=0.5, tensor_layout="NHD")
+        r = {"case": "knobs-NHD", "api_vs_api": metric(o, r_o), "shape_equal": list(o.shape) == list(r_o.shape)}
+        report["cases"].append(r)
+        print(json.dumps(r), flush=True)
+        # cdf entry point with its defaults, and the block-sparse entry point with a random mask
+        with RR.stable_sort(True):
+            r_o, r_s = ref_core.spas_sage2_attn_meansim_cuda(q, k, v, return_sparsity=True)
+        o, s_ = S.spas_sage2_attn_meansim_cuda(q, k, v, return_sparsity=True)
+        r = {"case": "knobs-cdf_defaults", "api_vs_api": metric(o, r_o), "sparsity_ref": r_s, "sparsity_ours": s_}
+        report["cases"].append(r)
+        print(json.dumps(r), flush=True)
+        mask = synthetic.bernoulli_block_mask(q.shape[0], H, q.shape[2], 0.4, 3, dev)
+        r_o, r_s = ref_core.block_sparse_sage2_attn_cuda(q, k, v, mask_id=mask, return_sparsity=True)
+        o, s_ = S.block_sparse_sage2_attn_cuda(q, k, v, mask_id=mask, return_sparsity=True)
+        r = {"case": "knobs-block_sparse", "api_vs_api": metric(o, r_o), "sparsity_ref": r_s, "sparsity_ours": s_}
+        report["cases"].append(r)
+        print(json.dumps(r), flush=True)
+        ops.check_device_status(dev)
+        del q, k, v
+        torch.cuda.empty_cache()
     if "sage1" in want:
         # Sage1 signatures (core.py:235-319): the reference runs its fp16-PV sm80 kernel with token-level causal masking;
         # this library serves them from the FP8-PV kernel. API against API, stable sort on the reference side.
