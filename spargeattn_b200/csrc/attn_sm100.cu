@@ -41,21 +41,26 @@ constexpr float kFastScaleLimit = 0.0078125f;  // 2^-7: bounds the fast path's p
 // PVF16: P and V in fp16 (tcgen05.mma kind::f16) instead of e4m3 -- the arithmetic of the reference's fp16-PV kernel
 // (csrc/qattn/qk_int_sv_f16_cuda_sm80.cuh), which its Sage1-signature entry points run. V then is the caller's fp16
 // tensor itself (no quantiser); a 64-key V tile is D/64 sub-tiles of [64 keys x 128 bytes] (64 channels each, 128B
-// swizzle), P is two sub-tiles of [128 rows x 128 bytes], one per block of a pair. The tiles are twice as large:
-// at D = 128 one CTA fits per SM, at D = 64 two (with two ring slots instead of four).
+// swizzle), P is two sub-tiles of [128 rows x 128 bytes], one per block of a pair. The tiles are twice as large,
+// so the rings are shorter (see kKTiles) to keep two CTAs per SM.
 template <int D, bool PVF16 = false>
 struct AttnShape {
-  static constexpr int kStagesK = (D == 128 || PVF16) ? 2 : 4;   // ring slots, each holding a PAIR of 64-key tiles
-  static constexpr int kStagesV = (D == 128 || PVF16) ? 2 : 4;
+  // K ring of single tiles (fp16 variant at D = 128): three 64-key tile slots instead of two pair slots, and one V
+  // pair slot, bring the CTA down to 105 KB of shared memory so that two fit per SM; a step's two K tiles are then not
+  // adjacent and QK^T is issued as two N = 64 instruction groups.
+  static constexpr bool kKTiles = PVF16 && D == 128;
+  static constexpr int kStagesK = kKTiles ? 3 : (D == 128 || PVF16) ? 2 : 4;   // ring slots: PAIRS of 64-key tiles (tiles if kKTiles)
+  static constexpr int kStagesV = kKTiles ? 1 : (D == 128 || PVF16) ? 2 : 4;
   static constexpr int kTileQ = 128 * D;
   static constexpr int kTileKV = 64 * D;
   static constexpr int kPairKV = 2 * kTileKV;
   static constexpr int kTileV = PVF16 ? 2 * kTileKV : kTileKV;
   static constexpr int kPairV = 2 * kTileV;
   static constexpr int kTileP = PVF16 ? 2 * 128 * 128 : 128 * 128;   // 128 rows x 128 keys of e4m3 / fp16
-  static constexpr int kSmemBytes = 1024 + kTileQ + kTileP + kStagesK * kPairKV + kStagesV * kPairV;
+  static constexpr int kRingK = kStagesK * (kKTiles ? kTileKV : kPairKV);
+  static constexpr int kSmemBytes = 1024 + kTileQ + kTileP + kRingK + kStagesV * kPairV;
   static constexpr int kTmemCols = 256;
-  static constexpr int kCtasPerSm = (PVF16 && D == 128) ? 1 : 2;   // fp16 tiles at D = 128: 145 KB of shared memory
+  static constexpr int kCtasPerSm = 2;
   static constexpr uint32_t kSwizzle = (D == 128) ? kSwizzle128B : kSwizzle64B;
 };
 
@@ -264,7 +269,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   uint8_t* sQ = smem;
   uint8_t* sP = smem + Shape::kTileQ;
   uint8_t* sK = sP + Shape::kTileP;                  // slot s: sK + s * kPairKV
-  uint8_t* sV = sK + SK * Shape::kPairKV;              // slot s: sV + s * kPairV
+  uint8_t* sV = sK + Shape::kRingK;                    // slot s: sV + s * kPairV
+  constexpr bool KT = Shape::kKTiles;
 
   __shared__ uint64_t bar_q, bar_k_full[SK], bar_k_empty[SK], bar_v_full[SV], bar_v_empty[SV], bar_s_full, bar_s_free,
       bar_p_ready, bar_o_done, bar_delta[2];
@@ -363,9 +369,23 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       ks_out = __shfl_sync(0xffffffffu, ks_lane, n - win);
       return __shfl_sync(0xffffffffu, jabs, n - win);
     };
-    int ok = 1, issued_k = 0, issued_v = 0;
+    int ok = 1, issued_k = 0, issued_v = 0, issued_tiles = 0;   // issued_tiles: K tiles requested in tile-ring mode
     auto load_pair = [&](const CUtensorMap* map, uint8_t* ring, uint64_t* full, uint64_t* empty, int stages, int s, int ja,
                          int jb, const int4* meta) {   // lane 0 only
+      if (KT && meta) {   // K ring of single tiles: block n of the row's live list goes to slot n % 3
+#pragma unroll
+        for (int blk = 0; blk < 2; blk++) {
+          if (blk == 1 && jb < 0) break;
+          const int n = 2 * s + blk, ts = n % 3;
+          if (n >= 3) ok = mbar_wait(&empty[ts], ((n / 3) - 1) & 1) ? 1 : 0;
+          if (!ok) return;
+          if (blk == 0) s_meta[s & 7] = *meta;   // see below: before the step's first K tile is requested
+          mbar_arrive_expect_tx(&full[ts], Shape::kTileKV);
+          tma_load_3d(ring + ts * Shape::kTileKV, map, &full[ts], 0, (blk ? jb : ja) * 64, bh);
+          issued_tiles = n + 1;
+        }
+        return;
+      }
       const int slot = s % stages;
       if (s >= stages) ok = mbar_wait(&empty[slot], ((s / stages) - 1) & 1) ? 1 : 0;
       if (!ok) return;
@@ -429,7 +449,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     if (!ok && lane == 0) {
       report(dev_status, SPARGE_DEV_TIMEOUT_PRODUCER);
       // drain our own copies before the CTA's shared memory goes away
-      for (int s = max(0, issued_k - SK); s < issued_k; s++) mbar_wait(&bar_k_full[s % SK], (s / SK) & 1);
+      if (KT) {
+        for (int n = max(0, issued_tiles - 3); n < issued_tiles; n++) mbar_wait(&bar_k_full[n % 3], (n / 3) & 1);
+      } else {
+        for (int s = max(0, issued_k - SK); s < issued_k; s++) mbar_wait(&bar_k_full[s % SK], (s / SK) & 1);
+      }
       for (int s = max(0, issued_v - SV); s < issued_v; s++) mbar_wait(&bar_v_full[s % SV], (s / SV) & 1);
     }
   } else if (warp == 9) {
@@ -469,7 +493,33 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         }
         started = 1;
       };
+      // waits for the K tiles of step s (one pair slot, or one or two tile slots of the tile ring)
+      auto wait_k = [&](int s) -> bool {
+        if (KT) {
+          const int nblk = min(2, cnt - 2 * s);
+          for (int blk = 0; blk < nblk; blk++) {
+            const int n = 2 * s + blk;
+            if (!mbar_wait(&bar_k_full[n % 3], (n / 3) & 1)) return false;
+          }
+          return true;
+        }
+        return mbar_wait(&bar_k_full[s % SK], (s / SK) & 1);
+      };
       auto issue_qk = [&](int s) {   // the caller has waited for the K tiles of step s
+        if (KT) {   // the step's tiles are not adjacent in the ring: one N = 64 instruction group per block
+          tc_fence_after();
+          const int nblk = min(2, cnt - 2 * s);
+          for (int blk = 0; blk < nblk; blk++) {
+            const int ts = (2 * s + blk) % 3;
+            const uint64_t kofs = (uint64_t)ts * (uint64_t)(Shape::kTileKV >> 4);
+#pragma unroll
+            for (int ks = 0; ks < D / 32; ks++)
+              mma_i8_ss(tbase + blk * 64, qd[ks], kd[ks] + kofs, idesc_qk1, ks > 0 ? 1u : 0u);
+            tc_commit(&bar_k_empty[ts]);
+          }
+          tc_commit(&bar_s_full);
+          return;
+        }
         const int slot = s % SK;
         tc_fence_after();
         const uint64_t kofs = (uint64_t)slot * kSlotStep;
@@ -479,14 +529,14 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         tc_commit(&bar_k_empty[slot]);
         tc_commit(&bar_s_full);
       };
-      if (ok) ok = mbar_wait(&bar_k_full[0], 0);
+      if (ok) ok = wait_k(0);
       if (ok) issue_qk(0);
       uint32_t o_started = 0;
       for (int s = 0; s < nsteps && ok; s++) {
         // Tiles arrive long before the softmax warps' hand-offs: their barriers are checked first, so that
         // only one wait stands between a hand-off and the MMAs it releases.
         if (s + 1 < nsteps) {
-          ok = mbar_wait(&bar_k_full[(s + 1) % SK], ((s + 1) / SK) & 1);
+          ok = wait_k(s + 1);
           if (!ok) break;
           ok = mbar_wait(&bar_s_free, s & 1);      // every softmax warp has read S(s) into registers
           if (!ok) break;
