@@ -200,8 +200,8 @@ int sparge_attn_fwd_gran(const int8_t* q_int8, const int8_t* k_int8, const uint8
  * (csrc/qattn/qk_int_sv_f16_cuda_sm80.cu, called by the Sage1-signature functions, spas_sage_attn/core.py:263,305),
  * with its arguments: v_f16 is the caller's fp16 V [B,H,N,D], contiguous and 16-byte aligned (no quantiser, no
  * v_scale, no padding: rows past N are read as zeros); per-block scales (qk_quant_gran 1); pvthreshd NULL = no skip
- * test, else the per-block test; pv_count, q_block_ranges as in sparge_attn_fwd_rows. The fp16 tiles are twice as
- * large, so one CTA runs per SM: about 1.6x the time of the FP8 kernel. */
+ * test, else the per-block test; pv_count, q_block_ranges as in sparge_attn_fwd_rows. About 1.2x (D = 128) and 1.06x
+ * (D = 64) the time of the FP8 kernel. */
 int sparge_attn_fwd_f16pv(const int8_t* q_int8, const int8_t* k_int8, const void* v_f16, void* o, const int32_t* lut,
                           const int32_t* valid, const float* pvthreshd, const float* q_scale, const float* k_scale,
                           int32_t* dev_status, int B, int H, int N, int D, int out_dtype, int is_causal, float sm_scale,

@@ -21,7 +21,7 @@ from . import ops
 SAGE2_TOKEN_LEVEL_CAUSAL = False
 
 # The Sage1-signature entry points of the reference (core.py:235-319) keep V in fp16 and run an fp16 P.V kernel.
-# True: they run the fp16-PV variant of the attention kernel here as well (one CTA per SM, about 1.6x the time);
+# True: they run the fp16-PV variant of the attention kernel here as well (about 1.2x the FP8 kernel's time);
 # False: they share the FP8-PV kernel of the Sage2 entry points (faster; output within cosine 0.9996 but only
 # 1.4-2.4 % relative L1 of the reference's, because V and P are rounded to e4m3).
 SAGE1_FP16_PV = True
