@@ -319,7 +319,7 @@ def main():
         # this library serves them from the FP8-PV kernel. API against API, stable sort on the reference side.
         ref_core = RR.load()["core"]
         jobs = [("small", small_inputs(1, 2, 3000, 128, torch.bfloat16, 14), False), ("small", small_inputs(2, 2, 1500, 64, torch.float16, 15), True)]
-        jobs += [(f"cfg{i}", tuple(t.cpu() for t in synthetic.workload_qkv(i, dev, heads=2)), synthetic.WORKLOADS[i]["causal"]) for i in (2, 3)]
+        jobs += [(f"cfg{i}", tuple(t.cpu() for t in synthetic.workload_qkv(i, dev, heads=2)), synthetic.WORKLOADS[i]["causal"]) for i in (2, 3, 4)]
         for tag, (q, k, v), causal in jobs:
             q, k, v = q.to(dev), k.to(dev), v.to(dev)
             with RR.stable_sort(True):
