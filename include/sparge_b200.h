@@ -208,6 +208,27 @@ int sparge_attn_fwd_f16pv(const int8_t* q_int8, const int8_t* k_int8, const void
                           long long o_stride_b, long long o_stride_h, long long o_stride_n, int32_t* pv_count,
                           const int32_t* q_block_ranges, int q_blocks_max, sparge_stream_t stream);
 
+/* The whole path of spas_sage2_attn_meansim_topk_cuda / spas_sage2_attn_meansim_cuda (spas_sage_attn/core.py:39-169) in
+ * one call: sparge_k_mean (if smooth_k), sparge_pool_quant for Q and K, sparge_select, sparge_quant_v and
+ * sparge_attn_fwd, issued in that order on `stream`, with every intermediate tensor carved out of `workspace`
+ * (device memory, 256-byte aligned, at least sparge_forward_workspace_bytes(B,H,N,D) bytes; reusable by the next call
+ * on the same stream). For hosts that pay per call (an interpreter): a small problem costs more to issue entry by
+ * entry than to run. Results are those of the separate entries.
+ *   q, k (dtype) and v (v_dtype): [B,H,N,D] views, strides in elements as {batch, head, token}, last dimension
+ *   contiguous; o like q. simthreshd1 [H]; exactly one of cdfthreshd / topk [H]; pvthreshd [H] or NULL (no skip test;
+ *   the LUT is then emitted best block first). is_causal: block-level causality of the selection; kernel_causal:
+ *   token-level masking inside the attention kernel (the reference's Sage2 entry points pass 0 there).
+ * sparge_forward_workspace_layout fills the 14 byte offsets of {km, k-mean scratch, pooled q, pooled k, sim_q, sim_k,
+ * q_int8, k_int8, q_scale, k_scale, lut, valid, v8, v_scale} inside the workspace (for return_sparsity, tests). */
+size_t sparge_forward_workspace_bytes(int B, int H, int N, int D);
+int sparge_forward_workspace_layout(int B, int H, int N, int D, size_t* offsets, int n_offsets);
+int sparge_meansim_forward(const void* q, const void* k, const void* v, void* o, const float* simthreshd1,
+                           const float* cdfthreshd, const float* topk, const float* pvthreshd, void* workspace,
+                           size_t workspace_bytes, int32_t* dev_status, int B, int H, int N, int D, int dtype, int v_dtype,
+                           int is_causal, int kernel_causal, int attention_sink, int smooth_k, float sm_scale,
+                           const long long* q_strides, const long long* k_strides, const long long* v_strides,
+                           const long long* o_strides, sparge_stream_t stream);
+
 /* Failure-detection self test: launches one warp that waits on a barrier nobody signals, for `slices` tries with
  * the suspend hint slice_ns (a try lasts about 4 us on a B200 whatever the hint; slices x max(slice_ns, 4000) may
  * not exceed 0.1 s), and writes SPARGE_DEV_TIMEOUT_SOFTMAX into

@@ -38,6 +38,10 @@ SIGNATURES = {
     "sparge_attn_fwd_gran": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _ll, _ll, _ll, _p, _p, _i,
                                   _i, _i, _p]),
     "sparge_attn_fwd_f16pv": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _ll, _ll, _ll, _p, _p, _i, _p]),
+    "sparge_forward_workspace_bytes": (ctypes.c_size_t, [_i, _i, _i, _i]),
+    "sparge_forward_workspace_layout": (_i, [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_size_t), _i]),
+    "sparge_meansim_forward": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, ctypes.c_size_t, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
+                                    _f, ctypes.POINTER(_ll), ctypes.POINTER(_ll), ctypes.POINTER(_ll), ctypes.POINTER(_ll), _p]),
     "sparge_peer_alloc": (_i, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
     "sparge_peer_free": (_i, [_p]),
     "sparge_peer_open": (_i, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),

@@ -10,7 +10,8 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsparge_b200.so")
-SOURCES = ["cabi.cu", "kmean.cu", "pool_quant.cu", "select.cu", "quant_v.cu", "attn_sm100.cu", "peer.cu", "tensor_peak.cu"]
+SOURCES = ["cabi.cu", "kmean.cu", "pool_quant.cu", "select.cu", "quant_v.cu", "attn_sm100.cu", "peer.cu", "tensor_peak.cu",
+           "forward.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xptxas", "-v"]
 

@@ -109,6 +109,9 @@ _SIDE_STREAMS = {}
 # worsen. Hence the window, in (batch * heads * tokens) rows.
 CONCURRENT_PREP_MIN_ROWS = 16384
 CONCURRENT_PREP_MAX_ROWS = 163840
+# Below the window the whole path is issued by one C call (sparge_meansim_forward): 0.14 ms of a [1, 4, 2048, 64] call
+# were the interpreter walking through nine wrappers.
+SINGLE_CALL_MAX_ROWS = CONCURRENT_PREP_MIN_ROWS
 
 
 def _side_streams(device):
@@ -213,6 +216,25 @@ def _meansim_attention(q, k, v, is_causal, scale, smooth_k, simthreshd1, cdfthre
     headdim = q.size(-1)
     assert headdim in [64, 128], "headdim should be in [64, 128]. For other headdim, you can use padding and specify the softmax scale."
     rows = q.size(0) * q.size(1) * q.size(2)
+    if rows < SINGLE_CALL_MAX_ROWS and q_block_ranges is None and not pv_fp16:
+        # a handful of short launches: issued by one C call, the interpreter's share of the time is what matters here
+        B_, H_, N_, _ = q.shape
+        thr = hyperparameter_check(simthreshd1, H_, q.device)
+        cdf = None if cdfthreshd is None else hyperparameter_check(cdfthreshd, H_, q.device)
+        tk = None if topk is None else hyperparameter_check(topk, H_, q.device)
+        assert (cdf is None) != (tk is None), "Only one of cdfthreshd and topk can be set."
+        pv = _pv_threshold_tensor(pvthreshd, H_, q.device)
+        o, ws, offs = ops.meansim_forward(q, k, v, _empty_like_layout(q), thr, cdf, tk, pv,
+                                          scale if scale is not None else 1.0 / (headdim ** 0.5), bool(is_causal),
+                                          kernel_causal, attention_sink, smooth_k)
+        if tensor_layout == 'NHD':
+            o = o.transpose(-2, -3)
+        if return_sparsity:
+            nq, nk = (N_ + 127) // 128, (N_ + 63) // 64
+            valid = ws[offs["valid"]:offs["valid"] + B_ * H_ * nq * 4].view(torch.int32)
+            denom = nk * nq * B_ * H_ if is_causal is False else (nk + 2) // 2 * nq * B_ * H_     # core.py:162-167
+            return o, (1 - valid.float().sum() / denom).item()
+        return o
     beside = CONCURRENT_PREP_MIN_ROWS <= rows <= CONCURRENT_PREP_MAX_ROWS
     s_q, s_v = _side_streams(q.device) if beside else (None, None)
     if pv_fp16:

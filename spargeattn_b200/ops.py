@@ -234,6 +234,36 @@ def attn_fwd_f16pv(q8, k8, v16, lut, valid, pvthreshd: Optional[torch.Tensor], q
     return (out, pv_count) if return_pv_count else out
 
 
+_forward_ws = {}
+WS_PARTS = ("km", "scratch", "pq", "pk", "sim_q", "sim_k", "q_int8", "k_int8", "q_scale", "k_scale", "lut", "valid", "v8", "v_scale")
+
+
+def meansim_forward(q, k, v, out, simthreshd1, cdfthreshd, topk, pvthreshd, sm_scale: float, is_causal: bool,
+                    kernel_causal: bool, attention_sink: bool, smooth_k: bool):
+    """The whole path in one C call (sparge_meansim_forward). q, k, v, out: [B,H,N,D] views with a contiguous last
+    dimension; the knob tensors are fp32 [H] on the device. Returns (out, workspace, offsets): the intermediates
+    (WS_PARTS, byte offsets) stay valid until the next call of this function on the same stream."""
+    import ctypes
+    _need_strided(q), _need_strided(k), _need_strided(v), _need_strided(out)
+    _need_cuda(simthreshd1, cdfthreshd, topk, pvthreshd)
+    B, H, N, D = q.shape
+    stream = _stream(q)
+    key = (q.device.index, stream)
+    nbytes = int(_cabi.lib.sparge_forward_workspace_bytes(B, H, N, D))
+    ws = _forward_ws.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = _forward_ws[key] = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    st3 = lambda t: (ctypes.c_longlong * 3)(t.stride(0), t.stride(1), t.stride(2))
+    _cabi.check(_cabi.lib.sparge_meansim_forward(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(simthreshd1), _ptr(cdfthreshd), _ptr(topk), _ptr(pvthreshd), _ptr(ws),
+        nbytes, _ptr(device_status_word(q.device)), B, H, N, D, _dt(q), _dt(v), int(bool(is_causal)), int(bool(kernel_causal)),
+        int(bool(attention_sink)), int(bool(smooth_k)), float(sm_scale), st3(q), st3(k), st3(v), st3(out), stream),
+        "sparge_meansim_forward")
+    offs = (ctypes.c_size_t * len(WS_PARTS))()
+    _cabi.check(_cabi.lib.sparge_forward_workspace_layout(B, H, N, D, offs, len(WS_PARTS)), "sparge_forward_workspace_layout")
+    return out, ws, dict(zip(WS_PARTS, list(offs)))
+
+
 def tensor_peak(kind: str = "i8", n: int = 128, ctas_per_sm: int = 2, target_ms: float = 50.0, device=None) -> dict:
     """Sustained tcgen05.mma rate of the current device for 8-bit operands (M = 128, N = n, K = 32 per
     instruction, operands resident in shared memory): {"tops", "ms", "kind", "n", "ctas_per_sm"}.

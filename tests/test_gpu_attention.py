@@ -184,8 +184,9 @@ def test_concurrent_preparation_gives_the_same_bytes():
     from spargeattn_b200 import core
     B, H, N, D = 1, 2, 3000, 128
     q, k, v = (t.cuda() for t in _inputs(B, H, N, D, torch.bfloat16, 20))
-    lo, hi = core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS
+    lo, hi, single = core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS, core.SINGLE_CALL_MAX_ROWS
     try:
+        core.SINGLE_CALL_MAX_ROWS = 0                                                      # entry by entry
         core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS = 1 << 40, 0          # one stream
         ref = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5)
         ref_c = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5, is_causal=True, pvthreshd=4.0)
@@ -200,9 +201,38 @@ def test_concurrent_preparation_gives_the_same_bytes():
         out_c = S.spas_sage2_attn_meansim_topk_cuda(q, k, v, topk=0.5, is_causal=True, pvthreshd=4.0)
         torch.cuda.synchronize()
     finally:
-        core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS = lo, hi
+        core.CONCURRENT_PREP_MIN_ROWS, core.CONCURRENT_PREP_MAX_ROWS, core.SINGLE_CALL_MAX_ROWS = lo, hi, single
     _status_ok()
     assert all(torch.equal(o, ref) for o in outs) and torch.equal(out_c, ref_c)
+
+
+@pytest.mark.parametrize("kw", [dict(topk=0.5), dict(topk=0.3, is_causal=True, attention_sink=True), dict(topk=0.6, pvthreshd=4.0),
+                                dict(cdfthreshd=0.9, simthreshd1=0.3), dict(topk=0.5, smooth_k=False), dict(topk=0.5, scale=0.07),
+                                dict(topk=0.4, tensor_layout="NHD")])
+@pytest.mark.parametrize("shape,dtype", [((2, 3, 1100, 64), torch.bfloat16), ((1, 2, 2048, 128), torch.float16)])
+def test_single_call_path_equals_the_entry_by_entry_path(kw, shape, dtype):
+    """Small problems are issued by one C call (sparge_meansim_forward) instead of nine wrappers: the same kernels in
+    the same order on the same stream, so the bytes are the same, for every knob, with and without return_sparsity."""
+    import spargeattn_b200 as S
+    from spargeattn_b200 import core
+    B, H, N, D = shape
+    q, k, v = (t.cuda() for t in _inputs(B, H, N, D, dtype, 23))
+    kw = dict(kw)
+    if kw.get("tensor_layout") == "NHD":
+        q, k, v = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+    fn = S.spas_sage2_attn_meansim_cuda if "cdfthreshd" in kw else S.spas_sage2_attn_meansim_topk_cuda
+    assert B * H * N < core.SINGLE_CALL_MAX_ROWS
+    one, sp_one = fn(q, k, v, return_sparsity=True, **kw)
+    one2 = fn(q, k, v, **kw)
+    single = core.SINGLE_CALL_MAX_ROWS
+    try:
+        core.SINGLE_CALL_MAX_ROWS = 0
+        sep, sp_sep = fn(q, k, v, return_sparsity=True, **kw)
+    finally:
+        core.SINGLE_CALL_MAX_ROWS = single
+    _status_ok()
+    assert torch.equal(one, sep) and torch.equal(one2, sep) and sp_one == sp_sep
+    assert one.shape == q.shape and one.stride() == sep.stride()
 
 
 def test_host_front_end_with_partially_owned_heads():
